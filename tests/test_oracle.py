@@ -1,0 +1,97 @@
+"""The CPU oracle against the golden vectors produced by the reference's own
+PyTorch path (tests/golden/make_golden.py).  No GPU needed."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import btp_oracle as O
+from conftest import OP_CASES, load_golden
+
+
+def _close(got, want, rtol, atol, what):
+    assert got.shape == want.shape, what
+    assert torch.allclose(got.double(), want.double(), rtol=rtol, atol=atol), (
+        f"{what}: max abs diff {(got.double() - want.double()).abs().max().item():.3e}"
+    )
+
+
+@pytest.mark.parametrize("case", OP_CASES)
+def test_forward_fp64_product_matches_reference(case):
+    g = load_golden(case)
+    y = O.btp_forward(g["a"].double(), g["x"].double(), 2, "product")
+    _close(y, g["y_ref64"], 1e-12, 1e-13, "y fp64")
+
+
+@pytest.mark.parametrize("case", [c for c in OP_CASES if c != "op_zeros_ones"])
+def test_forward_fp32_log_matches_reference(case):
+    g = load_golden(case)
+    y = O.btp_forward(g["a"], g["x"], 2, "log")
+    # same algorithm, same dtype, same summation order: agreement to rounding
+    _close(y, g["y_log32"], 2e-6, 2e-6, "y fp32 log")
+
+
+@pytest.mark.parametrize("case", OP_CASES)
+def test_forward_fp32_cumprod_matches_reference(case):
+    g = load_golden(case)
+    y = O.btp_forward(g["a"], g["x"], 2, "cumprod")
+    _close(y, g["y_lin32"], 2e-6, 2e-6, "y fp32 linear")
+
+
+@pytest.mark.parametrize("case", OP_CASES)
+def test_backward_closed_form_matches_reference_autograd_fp64(case):
+    g = load_golden(case)
+    dA, dx = O.btp_backward(g["a"].double(), g["x"].double(), g["dy"].double(), 2, "product")
+    _close(dx, g["dx_ref64"], 1e-11, 1e-12, "dx fp64")
+    _close(dA, g["dA_ref64"], 1e-10, 1e-11, "dA fp64")
+
+
+@pytest.mark.parametrize("case", [c for c in OP_CASES if c != "op_zeros_ones"])
+def test_backward_closed_form_fp32_log(case):
+    g = load_golden(case)
+    dA, dx = O.btp_backward(g["a"], g["x"], g["dy"], 2, "log")
+    assert O.rel_l2(dx, g["dx_log32"]) < 1e-6
+    assert O.rel_l2(dA, g["dA_log32"]) < 1e-5
+    assert O.rel_l2(dA, g["dA_ref64"]) < 1e-5
+
+
+@pytest.mark.parametrize("case", OP_CASES)
+def test_k1_local_pass_only(case):
+    g = load_golden(case)
+    y = O.btp_forward(g["a"].double(), g["x"].double(), 1, "product")
+    _close(y, g["y_k1_ref64"], 1e-12, 1e-13, "y k=1")
+    dA, dx = O.btp_backward(g["a"].double(), g["x"].double(), g["dy"].double(), 1, "product")
+    _close(dx, g["dx_k1_ref64"], 1e-11, 1e-12, "dx k=1")
+    _close(dA, g["dA_k1_ref64"], 1e-10, 1e-11, "dA k=1")
+
+
+def test_autograd_helper_agrees_with_closed_form():
+    g = load_golden("op_basic")
+    y, dA, dx = O.btp_forward_backward_autograd(g["a"].double(), g["x"].double(), g["dy"].double(), "product")
+    dA2, dx2 = O.btp_backward(g["a"].double(), g["x"].double(), g["dy"].double(), 2, "product")
+    _close(dA, dA2, 1e-10, 1e-11, "dA")
+    _close(dx, dx2, 1e-11, 1e-12, "dx")
+    _close(y, g["y_ref64"], 1e-12, 1e-13, "y")
+
+
+def test_one_hop_only():
+    """Changing block 0 changes block 1 and leaves block 2 bit-identical: the op is
+    a sliding window, not a full recurrence (reference.py:123-136)."""
+    g = load_golden("op_basic")
+    a, x = g["a"], g["x"]
+    y0 = O.btp_forward(a, x)
+    x2 = x.clone()
+    x2[..., :16] += 1.0
+    y1 = O.btp_forward(a, x2)
+    assert not torch.equal(y0[..., 16:32], y1[..., 16:32])
+    assert torch.equal(y0[..., 32:], y1[..., 32:])
+
+
+def test_shape_validation():
+    a = torch.rand(1, 2, 24)
+    x = torch.rand(1, 2, 16, 24)
+    with pytest.raises(ValueError):
+        O.btp_forward(a, x)
+    with pytest.raises(ValueError):
+        O.btp_forward(torch.rand(1, 3, 32), torch.rand(1, 2, 16, 32))
