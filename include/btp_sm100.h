@@ -1,0 +1,102 @@
+/*
+ * btp_sm100.h - C ABI of libbtp_sm100.so: block two-pass (BTP) sliding-window
+ * recurrence, forward and backward, hand-written for NVIDIA B200 (sm_100a).
+ *
+ * These entry points are what a foreign-function binding for the reference's
+ * native extension `spear._btp` would bind.  They replace
+ *   forward (coeff, x, y, checkpoint, k, wpb)             csrc/btp/_bindings.cu:76-150
+ *   backward(coeff, x, dy, checkpoint, dx, dA, k, wpb)    csrc/btp/_bindings.cu:152-229
+ * and the launchers behind them (csrc/btp/btp-forward.cu:462-527,
+ * csrc/btp/btp-backwards.cu:811-884).
+ *
+ * Contract shared by every entry point
+ *  - All tensor pointers are DEVICE pointers on the current CUDA device, dense
+ *    and contiguous:  x, y, dy, dx : [B, H, 16, L]   coeff, dA : [B, H, L]
+ *    checkpoint : [B, H, L/16, 16] float (slot j = carry into block j+1).
+ *  - L is a multiple of 16.  Pointers are 16-byte aligned.
+ *  - The library never allocates, frees or synchronises; it enqueues one kernel
+ *    on `stream` (a cudaStream_t passed as void*; NULL = the legacy default
+ *    stream) and returns.  Every element of y, dx and dA is written.
+ *  - Return value: BTP_OK or a negative BTP_ERR_* code; nothing is printed and
+ *    the process is never aborted.  btp_sm100_status_string() names a code and
+ *    btp_sm100_last_error() gives the detail recorded by the calling thread's
+ *    most recent failing call.
+ *  - Calls are re-entrant and thread-safe.
+ */
+#ifndef BTP_SM100_H_
+#define BTP_SM100_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BTP_SM100_ABI_VERSION 1
+
+/* status codes */
+#define BTP_OK 0
+#define BTP_ERR_NULL_POINTER (-1)
+#define BTP_ERR_BAD_SHAPE (-2)      /* B, H, L <= 0, L % 16 != 0, or sizes beyond int32 tile counts */
+#define BTP_ERR_BAD_ORDER (-3)      /* k not in {1, 2} */
+#define BTP_ERR_BAD_DTYPE (-4)
+#define BTP_ERR_MISALIGNED (-5)     /* a pointer is not 16-byte aligned */
+#define BTP_ERR_CUDA (-6)           /* a CUDA runtime / driver call failed; see btp_sm100_last_error() */
+#define BTP_ERR_UNSUPPORTED_DEVICE (-7) /* current device is not compute capability 10.x */
+#define BTP_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel gave up (btp_sm100_device_status) */
+
+/* dtype tags */
+#define BTP_DTYPE_BF16 0        /* x, y, dy, dx, coeff */
+#define BTP_DTYPE_F32 1         /* y, dy;  coeff given in linear space as float */
+#define BTP_DTYPE_F32_LOG 2     /* coeff only: natural log of the coefficient, float (superset of the reference) */
+
+/*
+ * Forward:  y = btp(coeff, x).
+ * Replaces spear._btp.forward (csrc/btp/_bindings.cu:76-150 -> btp-forward.cu:85-457).
+ *   coeff        [B,H,L]      coeff_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F32 | BTP_DTYPE_F32_LOG
+ *   x            [B,H,16,L]   bf16
+ *   y            [B,H,16,L]   out_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F32
+ *   checkpoint   [B,H,L/16,16] float, or NULL.  When given and k == 2, slot j < L/16-1 receives the
+ *                block-local last token of block j, exactly the tensor the reference's forward
+ *                saves (btp-forward.cu:369-373).  The backward below does not need it.
+ *   k            2 = local pass + one-hop carry, 1 = local pass only (interface.py:164-188)
+ */
+int btp_sm100_forward(const void* coeff, const void* x, void* y, float* checkpoint,
+                      int B, int H, int L, int k, int coeff_dtype, int out_dtype, void* stream);
+
+/*
+ * Backward:  (dx, dA) for upstream gradient dy.
+ * Replaces spear._btp.backward (csrc/btp/_bindings.cu:152-229 -> btp-backwards.cu:165-808).
+ *   dy           [B,H,16,L]   dy_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F32
+ *   checkpoint   accepted for signature compatibility and ignored (may be NULL): the carry is
+ *                recomputed from x and coeff, which costs no extra memory traffic.
+ *   dx           [B,H,16,L]   bf16
+ *   dA           [B,H,L]      float, gradient w.r.t. the linear coefficient (w.r.t. the log
+ *                coefficient when coeff_dtype == BTP_DTYPE_F32_LOG)
+ */
+int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const float* checkpoint,
+                       void* dx, float* dA, int B, int H, int L, int k,
+                       int coeff_dtype, int dy_dtype, void* stream);
+
+/* Name of a status code ("BTP_OK", "BTP_ERR_BAD_SHAPE", ...).  Never NULL. */
+const char* btp_sm100_status_string(int status);
+
+/* Detail text of the calling thread's most recent failing call ("" if none).  Never NULL. */
+const char* btp_sm100_last_error(void);
+
+/*
+ * Synchronises `stream` and reads the device-side error word that the kernels set when one of
+ * their bounded waits gives up.  Returns BTP_OK, BTP_ERR_DEVICE_TIMEOUT or BTP_ERR_CUDA.
+ * `detail`, if not NULL, receives 4 words: {code, blockIdx.x, warp, chunk}.  The word is cleared.
+ * Not on the hot path: the forward/backward calls themselves never synchronise.
+ */
+int btp_sm100_device_status(void* stream, unsigned int* detail);
+
+/* Number of kernels this library has launched in this process (all threads). */
+unsigned long long btp_sm100_launch_count(void);
+
+/* ABI version of the loaded library (BTP_SM100_ABI_VERSION at build time). */
+int btp_sm100_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BTP_SM100_H_ */

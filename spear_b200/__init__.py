@@ -1,0 +1,23 @@
+"""spear_b200: the block two-pass (BTP) hot path of SPEAR, hand-written for NVIDIA B200 (sm_100a).
+
+    from spear_b200.ops.btp import btp          # same signature as spear.ops.btp.btp
+    from spear_b200.nn.phalanx import Phalanx   # same constructor / state_dict as spear.nn.phalanx.Phalanx
+
+The native library is loaded on first use; there is no CPU or PyTorch fallback.
+"""
+
+__version__ = "0.1.0"
+
+__all__ = ["btp", "Phalanx", "SigmoidA"]
+
+
+def __getattr__(name):  # lazy: importing the package must not require torch ops to be registered
+    if name == "btp":
+        from .ops.btp import btp
+
+        return btp
+    if name in ("Phalanx", "SigmoidA"):
+        from .nn import phalanx
+
+        return getattr(phalanx, name)
+    raise AttributeError(name)

@@ -1,0 +1,88 @@
+"""Drop-in for the reference's compiled extension module ``spear._btp``.
+
+Same two functions, same positional arguments, same in-place contract
+(csrc/btp/_bindings.cu:76-229, 240-243):
+
+    forward (coeff, x, y, checkpoint, k, wpb) -> None
+    backward(coeff, x, dy, checkpoint, dx, dA, k, wpb) -> None
+
+so that ``sys.modules["spear._btp"] = spear_b200._btp`` makes the unmodified
+reference package run on these kernels.  The checks mirror the reference's
+TORCH_CHECKs (_bindings.cu:19-60) and add the ones it lacks (coeff shape,
+contiguity).  ``wpb`` is validated and otherwise ignored: the sm_100a kernels
+pick their own launch shape.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+DH = 16
+BLK = 16
+SUPPORTED_WPB = (4, 8, 16, 32)
+
+_TAG = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None or t.numel() == 0 else t.data_ptr())
+
+
+def _check_common(coeff: torch.Tensor, x: torch.Tensor, k: int, wpb: int) -> tuple[int, int, int]:
+    _require(x.is_cuda and coeff.is_cuda, "BTP tensors must be CUDA tensors (there is no CPU path)")
+    _require(x.dim() == 4 and x.shape[2] == DH, f"x must be [B, H, {DH}, L], got {tuple(x.shape)}")
+    B, H, _, L = x.shape
+    _require(tuple(coeff.shape) == (B, H, L), f"coeff must be [B, H, L] = {(B, H, L)}, got {tuple(coeff.shape)}")
+    _require(L % BLK == 0, f"Length L must be multiple of {BLK}")
+    _require(k in (1, 2), "k must be 1 or 2")
+    _require(wpb in SUPPORTED_WPB, f"WPB must be one of {list(SUPPORTED_WPB)}")
+    _require(x.dtype == torch.bfloat16, f"x must be bfloat16 (got {x.dtype}); this build is bf16-only")
+    _require(coeff.dtype in (torch.bfloat16, torch.float32), f"coeff must be bfloat16 or float32 (got {coeff.dtype})")
+    _require(x.is_contiguous() and coeff.is_contiguous(), "coeff and x must be contiguous")
+    _require(coeff.device == x.device, "coeff and x must be on the same device")
+    return B, H, L
+
+
+def forward(coeff, x, y, checkpoint, k: int, wpb: int, *, log_coeff: bool = False) -> None:
+    """y <- btp(coeff, x); optionally fills the reference's carry checkpoint."""
+    B, H, L = _check_common(coeff, x, k, wpb)
+    _require(y.shape == x.shape and y.is_contiguous() and y.device == x.device, "y must match x and be contiguous")
+    _require(y.dtype in _TAG, f"y must be bfloat16 or float32 (got {y.dtype})")
+    if checkpoint is not None and checkpoint.numel():
+        _require(checkpoint.dtype == torch.float32 and checkpoint.is_contiguous(), "checkpoint must be contiguous float32")
+        _require(tuple(checkpoint.shape) == (B, H, L // BLK, DH), "checkpoint must be [B, H, L/16, 16]")
+    ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
+    _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = _lib.load().btp_sm100_forward(
+            _ptr(coeff), _ptr(x), _ptr(y), _ptr(checkpoint), B, H, L, int(k), ctag, _TAG[y.dtype], ctypes.c_void_p(stream)
+        )
+    _lib.check(rc, "btp_sm100_forward")
+
+
+def backward(coeff, x, dy, checkpoint, dx, dA, k: int, wpb: int, *, log_coeff: bool = False) -> None:
+    """dx, dA <- gradients for upstream dy.  `checkpoint` is accepted and ignored."""
+    B, H, L = _check_common(coeff, x, k, wpb)
+    _require(dy.shape == x.shape and dy.is_contiguous() and dy.device == x.device, "dy must match x and be contiguous")
+    _require(dy.dtype in _TAG, f"dy must be bfloat16 or float32 (got {dy.dtype})")
+    _require(dx.shape == x.shape and dx.dtype == x.dtype and dx.is_contiguous(), "dx must match x (shape, dtype)")
+    _require(tuple(dA.shape) == (B, H, L) and dA.dtype == torch.float32 and dA.is_contiguous(), "dA must be float32 [B, H, L]")
+    ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
+    _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = _lib.load().btp_sm100_backward(
+            _ptr(coeff), _ptr(x), _ptr(dy), _ptr(None), _ptr(dx), _ptr(dA), B, H, L, int(k), ctag, _TAG[dy.dtype],
+            ctypes.c_void_p(stream),
+        )
+    _lib.check(rc, "btp_sm100_backward")

@@ -1,0 +1,348 @@
+// libbtp_sm100.so - C ABI, argument checks, TMA descriptors and launches for the BTP kernels.
+// Host-side counterpart of the reference's csrc/btp/_bindings.cu:19-229 and of the launchers
+// csrc/btp/btp-forward.cu:462-527, csrc/btp/btp-backwards.cu:811-884; no torch types here.
+#include "../../include/btp_sm100.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "btp_kernels.cuh"
+
+namespace {
+
+using namespace btp;
+
+thread_local char tls_error[512] = "";
+std::atomic<unsigned long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define BTP_CUDA_TRY(expr)                                                                      \
+  do {                                                                                          \
+    cudaError_t _e = (expr);                                                                    \
+    if (_e != cudaSuccess) return fail(BTP_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e));  \
+  } while (0)
+
+// ------------------------------------------------------------------ driver entry point for TMA descriptors
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+// [rows = BH*16][cols = L] tensor, box = 16 rows x `box_cols` (one 128-byte swizzle span).
+int make_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint32_t esz = f32 ? 4 : 2;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(L) * esz};
+  const cuuint32_t box[2] = {128u / esz, 16u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return BTP_OK;
+}
+
+// ------------------------------------------------------------------ per-device launch facts, computed once
+struct DeviceInfo {
+  bool ready = false;
+  int sms = 0;
+  int cc_major = 0;
+};
+DeviceInfo g_dev[64];
+std::mutex g_dev_mutex;
+
+int device_info(int* dev_out, DeviceInfo* info) {
+  int dev = 0;
+  BTP_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(BTP_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_dev[dev].ready) {
+    BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+    BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    g_dev[dev].ready = true;
+  }
+  *dev_out = dev;
+  *info = g_dev[dev];
+  if (info->cc_major != 10) {
+    return fail(BTP_ERR_UNSUPPORTED_DEVICE, "device %d has compute capability %d.x; this library is built for 10.x only",
+                dev, info->cc_major);
+  }
+  return BTP_OK;
+}
+
+// One launchable kernel instance: sets its shared-memory limit and resident-CTA count once per device.
+template <class KERNEL>
+struct Launcher {
+  KERNEL kernel;
+  int smem_bytes;
+  int threads;
+  int warps;
+  int ctas_per_sm[64];
+  std::mutex mu;
+  Launcher(KERNEL k, int smem, int nthreads) : kernel(k), smem_bytes(smem), threads(nthreads), warps(nthreads / 32) {
+    for (int& c : ctas_per_sm) c = -1;
+  }
+  int prepare(int dev, int* ctas) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (ctas_per_sm[dev] < 0) {
+      BTP_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+      int occ = 0;
+      BTP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem_bytes));
+      if (occ < 1) return fail(BTP_ERR_CUDA, "kernel does not fit on an SM (%d bytes of shared memory)", smem_bytes);
+      ctas_per_sm[dev] = occ;
+    }
+    *ctas = ctas_per_sm[dev];
+    return BTP_OK;
+  }
+  // persistent grid: every resident warp gets a contiguous share of the chunks
+  int grid_for(int sms, int ctas, int total_chunks) const {
+    long long want = (static_cast<long long>(total_chunks) + warps - 1) / warps;
+    long long cap = static_cast<long long>(sms) * ctas;
+    return static_cast<int>(want < cap ? want : cap);
+  }
+};
+
+// Tuning variant (chunk width / ring depth / warps per CTA); chosen once from BTP_SM100_VARIANT.
+int variant() {
+  static int v = [] {
+    const char* e = getenv("BTP_SM100_VARIANT");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
+struct Dims {
+  int B, H, L;
+  long long BH;
+  int ncs;
+  int total_chunks;
+};
+
+int check_common(const char* fn, int B, int H, int L, int k, int coeff_dtype, Dims* d) {
+  if (B <= 0 || H <= 0 || L <= 0) return fail(BTP_ERR_BAD_SHAPE, "%s: B, H, L must be positive (got %d, %d, %d)", fn, B, H, L);
+  if (L % 16 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: L must be a multiple of 16 (got %d)", fn, L);
+  if (k != 1 && k != 2) return fail(BTP_ERR_BAD_ORDER, "%s: k must be 1 or 2 (got %d)", fn, k);
+  if (coeff_dtype != BTP_DTYPE_BF16 && coeff_dtype != BTP_DTYPE_F32 && coeff_dtype != BTP_DTYPE_F32_LOG)
+    return fail(BTP_ERR_BAD_DTYPE, "%s: unsupported coefficient dtype tag %d", fn, coeff_dtype);
+  d->B = B; d->H = H; d->L = L;
+  d->BH = static_cast<long long>(B) * H;
+  if (d->BH * 16 > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: B*H*16 = %lld rows exceeds the 2^31-1 limit", fn, d->BH * 16);
+  return BTP_OK;
+}
+
+int set_chunks(const char* fn, Dims* d, int TL) {
+  d->ncs = (d->L + TL - 1) / TL;
+  const long long total = d->BH * d->ncs;
+  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld chunks exceed the 2^31-1 limit", fn, total);
+  d->total_chunks = static_cast<int>(total);
+  return BTP_OK;
+}
+
+bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+// ------------------------------------------------------------------ forward dispatch
+template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
+int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
+  using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, false, false>;
+  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, NBOX, STAGES, WARPS>;
+  static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = L.prepare(dev, &ctas))) return rc;
+  if ((rc = set_chunks("btp_sm100_forward", &d, LAYOUT::kTL))) return rc;
+  CUtensorMap tm_x, tm_y;
+  if ((rc = make_map(&tm_x, x, false, d.BH * 16, d.L))) return rc;
+  if (OUT_F32) {
+    tm_y = tm_x;  // unused by the kernel
+  } else if ((rc = make_map(&tm_y, y, false, d.BH * 16, d.L))) {
+    return rc;
+  }
+  KernelParams p{};
+  p.coeff = coeff; p.x = x; p.out_f32 = y; p.ckpt = ckpt;
+  p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
+  const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
+  kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_y, p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+
+template <int COEF, bool OUT_F32, bool CKPT>
+int forward_variant(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t s) {
+  if constexpr (COEF == kCoefBf16 && !OUT_F32 && !CKPT) {  // the benchmarked path has tuning variants
+    switch (variant()) {
+      case 1: return launch_forward<COEF, OUT_F32, CKPT, 2, 4, 4>(coeff, x, y, ckpt, d, k, s);
+      case 2: return launch_forward<COEF, OUT_F32, CKPT, 1, 4, 4>(coeff, x, y, ckpt, d, k, s);
+      case 3: return launch_forward<COEF, OUT_F32, CKPT, 1, 6, 4>(coeff, x, y, ckpt, d, k, s);
+      case 4: return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 8>(coeff, x, y, ckpt, d, k, s);
+      default: break;
+    }
+  }
+  return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 4>(coeff, x, y, ckpt, d, k, s);
+}
+
+template <int COEF>
+int forward_coef(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, int out_dtype, cudaStream_t s) {
+  const bool f32 = out_dtype == BTP_DTYPE_F32;
+  const bool ck = ckpt != nullptr && k == 2;
+  if (f32) return ck ? forward_variant<COEF, true, true>(coeff, x, y, ckpt, d, k, s)
+                     : forward_variant<COEF, true, false>(coeff, x, y, ckpt, d, k, s);
+  return ck ? forward_variant<COEF, false, true>(coeff, x, y, ckpt, d, k, s)
+            : forward_variant<COEF, false, false>(coeff, x, y, ckpt, d, k, s);
+}
+
+// ------------------------------------------------------------------ backward dispatch
+template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
+int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
+                    cudaStream_t stream) {
+  using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, true, DY_F32>;
+  auto kern = btp_backward_kernel<COEF, DY_F32, NBOX, STAGES, WARPS>;
+  static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = L.prepare(dev, &ctas))) return rc;
+  if ((rc = set_chunks("btp_sm100_backward", &d, LAYOUT::kTL))) return rc;
+  CUtensorMap tm_x, tm_dy, tm_dx;
+  if ((rc = make_map(&tm_x, x, false, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_dy, dy, DY_F32, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_dx, dx, false, d.BH * 16, d.L))) return rc;
+  KernelParams p{};
+  p.coeff = coeff; p.x = x; p.dy = dy; p.dA = dA;
+  p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
+  const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
+  kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_dy, tm_dx, p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+
+template <int COEF, bool DY_F32>
+int backward_variant(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k, cudaStream_t s) {
+  if constexpr (COEF == kCoefBf16 && !DY_F32) {
+    switch (variant()) {
+      case 1: return launch_backward<COEF, DY_F32, 2, 4, 2>(coeff, x, dy, dx, dA, d, k, s);
+      case 2: return launch_backward<COEF, DY_F32, 1, 4, 4>(coeff, x, dy, dx, dA, d, k, s);
+      case 3: return launch_backward<COEF, DY_F32, 1, 6, 4>(coeff, x, dy, dx, dA, d, k, s);
+      case 4: return launch_backward<COEF, DY_F32, 2, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
+      default: break;
+    }
+  }
+  return launch_backward<COEF, DY_F32, 2, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
+}
+
+}  // namespace
+
+// ====================================================================== C ABI
+extern "C" {
+
+int btp_sm100_forward(const void* coeff, const void* x, void* y, float* checkpoint, int B, int H, int L, int k,
+                      int coeff_dtype, int out_dtype, void* stream) {
+  Dims d{};
+  int rc = check_common("btp_sm100_forward", B, H, L, k, coeff_dtype, &d);
+  if (rc) return rc;
+  if (out_dtype != BTP_DTYPE_BF16 && out_dtype != BTP_DTYPE_F32)
+    return fail(BTP_ERR_BAD_DTYPE, "btp_sm100_forward: unsupported output dtype tag %d", out_dtype);
+  if (!coeff || !x || !y) return fail(BTP_ERR_NULL_POINTER, "btp_sm100_forward: coeff, x and y must not be NULL");
+  if (misaligned(coeff) || misaligned(x) || misaligned(y) || misaligned(checkpoint))
+    return fail(BTP_ERR_MISALIGNED, "btp_sm100_forward: every pointer must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (coeff_dtype) {
+    case BTP_DTYPE_BF16: return forward_coef<kCoefBf16>(coeff, x, y, checkpoint, d, k, out_dtype, s);
+    case BTP_DTYPE_F32: return forward_coef<kCoefF32>(coeff, x, y, checkpoint, d, k, out_dtype, s);
+    default: return forward_coef<kCoefF32Log>(coeff, x, y, checkpoint, d, k, out_dtype, s);
+  }
+}
+
+int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const float* checkpoint, void* dx, float* dA,
+                       int B, int H, int L, int k, int coeff_dtype, int dy_dtype, void* stream) {
+  (void)checkpoint;  // the carry is recomputed; see the header
+  Dims d{};
+  int rc = check_common("btp_sm100_backward", B, H, L, k, coeff_dtype, &d);
+  if (rc) return rc;
+  if (dy_dtype != BTP_DTYPE_BF16 && dy_dtype != BTP_DTYPE_F32)
+    return fail(BTP_ERR_BAD_DTYPE, "btp_sm100_backward: unsupported dy dtype tag %d", dy_dtype);
+  if (!coeff || !x || !dy || !dx || !dA)
+    return fail(BTP_ERR_NULL_POINTER, "btp_sm100_backward: coeff, x, dy, dx and dA must not be NULL");
+  if (misaligned(coeff) || misaligned(x) || misaligned(dy) || misaligned(dx) || misaligned(dA))
+    return fail(BTP_ERR_MISALIGNED, "btp_sm100_backward: every pointer must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool f32 = dy_dtype == BTP_DTYPE_F32;
+  switch (coeff_dtype) {
+    case BTP_DTYPE_BF16:
+      return f32 ? backward_variant<kCoefBf16, true>(coeff, x, dy, dx, dA, d, k, s)
+                 : backward_variant<kCoefBf16, false>(coeff, x, dy, dx, dA, d, k, s);
+    case BTP_DTYPE_F32:
+      return f32 ? backward_variant<kCoefF32, true>(coeff, x, dy, dx, dA, d, k, s)
+                 : backward_variant<kCoefF32, false>(coeff, x, dy, dx, dA, d, k, s);
+    default:
+      return f32 ? backward_variant<kCoefF32Log, true>(coeff, x, dy, dx, dA, d, k, s)
+                 : backward_variant<kCoefF32Log, false>(coeff, x, dy, dx, dA, d, k, s);
+  }
+}
+
+const char* btp_sm100_status_string(int status) {
+  switch (status) {
+    case BTP_OK: return "BTP_OK";
+    case BTP_ERR_NULL_POINTER: return "BTP_ERR_NULL_POINTER";
+    case BTP_ERR_BAD_SHAPE: return "BTP_ERR_BAD_SHAPE";
+    case BTP_ERR_BAD_ORDER: return "BTP_ERR_BAD_ORDER";
+    case BTP_ERR_BAD_DTYPE: return "BTP_ERR_BAD_DTYPE";
+    case BTP_ERR_MISALIGNED: return "BTP_ERR_MISALIGNED";
+    case BTP_ERR_CUDA: return "BTP_ERR_CUDA";
+    case BTP_ERR_UNSUPPORTED_DEVICE: return "BTP_ERR_UNSUPPORTED_DEVICE";
+    case BTP_ERR_DEVICE_TIMEOUT: return "BTP_ERR_DEVICE_TIMEOUT";
+    default: return "BTP_ERR_UNKNOWN";
+  }
+}
+
+const char* btp_sm100_last_error(void) { return tls_error; }
+
+int btp_sm100_device_status(void* stream, unsigned int* detail) {
+  BTP_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  unsigned int words[4] = {0, 0, 0, 0};
+  BTP_CUDA_TRY(cudaMemcpyFromSymbol(words, btp::g_btp_device_error, sizeof(words)));
+  if (detail) memcpy(detail, words, sizeof(words));
+  if (words[0] == 0) return BTP_OK;
+  const unsigned int zero[4] = {0, 0, 0, 0};
+  BTP_CUDA_TRY(cudaMemcpyToSymbol(btp::g_btp_device_error, zero, sizeof(zero)));
+  return fail(BTP_ERR_DEVICE_TIMEOUT, "a kernel wait gave up: block %u warp %u chunk %u", words[1], words[2], words[3]);
+}
+
+unsigned long long btp_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int btp_sm100_abi_version(void) { return BTP_SM100_ABI_VERSION; }
+
+}  // extern "C"
