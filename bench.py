@@ -163,6 +163,7 @@ def run_reference_arm(args, rank):
 
 
 def main():
+    global B
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -174,7 +175,6 @@ def main():
     ap.add_argument("--sets", type=int, default=3, help="rotating input/output sets")
     args = ap.parse_args()
 
-    global B
     B = args.batch
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
