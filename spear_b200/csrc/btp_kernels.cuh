@@ -7,7 +7,7 @@
 //   Lmat[r,c] = 2^(T_r - T_c) for c <= r, else 0         P[r] = 2^(T_r)
 //   v_i       = x_i . Lmat^T                             (local pass, tensor cores)
 //   y_i       = v_i + P (x) carry_i,   carry_i = v_{i-1}[:,15]   (ONE hop, never the corrected value)
-//   gw_i      = dy_i . Lmat,  dCarry_i = 2^(T_0) gw_i[:,0]
+//   gw_i      = dy_i . Lmat,  dCarry_i = P[0] gw_i[:,0]
 //   dx_i[:,c] = gw_i[:,c] + Lmat[15,c] dCarry_{i+1}
 //   dA_i[t]   = sum_ch v_i[ch,t-1] dx_i[ch,t] + P[t-1] sum_ch gw_i[ch,t] carry_i[ch]
 //               (v[:, -1] = 0, P[-1] = 1; no division by a anywhere)
@@ -18,6 +18,9 @@
 //   * Every WARP owns a private ring of STAGES chunk buffers with its own mbarriers and walks a
 //     contiguous range of chunks.  No block-wide or grid-wide synchronisation exists, so no warp
 //     ever waits for another warp; the only waits are on the warp's own TMA loads (bounded).
+//   * Once per chunk the warp turns the coefficients into the per-token tables the blocks need
+//     (T, P, and for backward P shifted by one token and the last Lmat row), so that the per-block
+//     work is the Lmat fragment (6 exponentials per lane), the tensor-core products and FMAs.
 //   * The carry stays in registers while a warp walks along a sequence.  Where a warp's range
 //     starts (ends) inside a sequence the neighbouring block is re-read from global memory
 //     (16x16 values, a "halo") and its carry (dCarry) recomputed, so no seam ever drops a carry.
@@ -69,7 +72,9 @@ __device__ __forceinline__ float coef_log2(float a) {
   }
 }
 
-// Shared-memory carve-up of one CTA.  Every warp owns STAGES stages.
+// Shared-memory carve-up of one CTA.  Every warp owns STAGES stages; a stage holds the tiles of one
+// chunk ("big": x, and dy for backward) and its per-token float tables ("small", kTables x TL floats):
+//   forward : T, P                 backward: T, Pshift (P[t-1], 1 at t=0), L15 (last Lmat row), dA staging
 template <int NBOX, int STAGES, int WARPS, bool BWD, bool DY_F32>
 struct SmemLayout {
   static constexpr int kTL = 64 * NBOX;                 // tokens per chunk
@@ -77,9 +82,8 @@ struct SmemLayout {
   static constexpr int kXBytes = NBOX * 2048;           // [16][64] bf16 per box
   static constexpr int kDyBytes = BWD ? (DY_F32 ? NBOX * 4096 : NBOX * 2048) : 0;
   static constexpr int kBigPerStage = kXBytes + kDyBytes;  // multiple of 1024 (swizzle atom)
-  static constexpr int kTBytes = kTL * 4;               // coefficient landing zone, then T (float)
-  static constexpr int kDaBytes = BWD ? kTL * 4 : 0;
-  static constexpr int kSmallPerStage = kTBytes + kDaBytes;
+  static constexpr int kTables = BWD ? 4 : 2;
+  static constexpr int kSmallPerStage = kTables * kTL * 4;
   static constexpr int kBigTotal = WARPS * STAGES * kBigPerStage;
   static constexpr int kSmallTotal = WARPS * STAGES * kSmallPerStage;
   static constexpr int kBarTotal = WARPS * STAGES * 8;
@@ -87,30 +91,26 @@ struct SmemLayout {
 };
 
 // Per-warp view of its stages.
-template <class LAYOUT, int STAGES>
+template <class LAYOUT>
 struct WarpSmem {
   uint32_t big;    // shared-space address of stage 0 of the tile buffers
-  uint32_t small;  // ... of the T / dA buffers
+  uint32_t small;  // ... of the tables
   uint32_t bars;   // ... of the mbarriers
   unsigned char* small_ptr;  // generic pointer to `small`
   __device__ __forceinline__ uint32_t x(int s) const { return big + s * LAYOUT::kBigPerStage; }
   __device__ __forceinline__ uint32_t dy(int s) const { return x(s) + LAYOUT::kXBytes; }
-  __device__ __forceinline__ uint32_t t_addr(int s) const { return small + s * LAYOUT::kSmallPerStage; }
-  __device__ __forceinline__ float* t_ptr(int s) const {
+  __device__ __forceinline__ uint32_t tab_addr(int s) const { return small + s * LAYOUT::kSmallPerStage; }
+  __device__ __forceinline__ float* tab_ptr(int s) const {
     return reinterpret_cast<float*>(small_ptr + s * LAYOUT::kSmallPerStage);
-  }
-  __device__ __forceinline__ uint32_t da_addr(int s) const { return t_addr(s) + LAYOUT::kTBytes; }
-  __device__ __forceinline__ float* da_ptr(int s) const {
-    return reinterpret_cast<float*>(small_ptr + s * LAYOUT::kSmallPerStage + LAYOUT::kTBytes);
   }
   __device__ __forceinline__ uint32_t bar(int s) const { return bars + s * 8; }
 };
 
-template <class LAYOUT, int STAGES, int WARPS>
-__device__ __forceinline__ WarpSmem<LAYOUT, STAGES> carve_smem(unsigned char* raw, int warp) {
+template <class LAYOUT, int STAGES>
+__device__ __forceinline__ WarpSmem<LAYOUT> carve_smem(unsigned char* raw, int warp) {
   const uint32_t base = smem_u32(raw);
   const uint32_t pad = (1024u - (base & 1023u)) & 1023u;
-  WarpSmem<LAYOUT, STAGES> w;
+  WarpSmem<LAYOUT> w;
   w.big = base + pad + warp * STAGES * LAYOUT::kBigPerStage;
   w.small = base + pad + LAYOUT::kBigTotal + warp * STAGES * LAYOUT::kSmallPerStage;
   w.small_ptr = raw + pad + LAYOUT::kBigTotal + warp * STAGES * LAYOUT::kSmallPerStage;
@@ -118,53 +118,97 @@ __device__ __forceinline__ WarpSmem<LAYOUT, STAGES> carve_smem(unsigned char* ra
   return w;
 }
 
-struct ChunkPos {
+// Position of a chunk; walks forward one chunk at a time (no division after the first).
+struct ChunkCursor {
   int bh;  // sequence index
   int cs;  // chunk index inside the sequence
-  int c0;  // first token
-  int nt;  // 16-token blocks in this chunk (ragged last chunk: fewer)
+  __device__ __forceinline__ ChunkCursor(int id, int ncs) : bh(id / ncs), cs(id - (id / ncs) * ncs) {}
+  __device__ __forceinline__ void next(int ncs) {
+    if (++cs == ncs) {
+      cs = 0;
+      ++bh;
+    }
+  }
 };
 
 template <int TL>
-__device__ __forceinline__ ChunkPos chunk_pos(int id, int ncs, int L) {
-  ChunkPos p;
-  p.bh = id / ncs;
-  p.cs = id - p.bh * ncs;
-  p.c0 = p.cs * TL;
-  const int left = (L - p.c0) >> 4;
-  p.nt = left < TL / 16 ? left : TL / 16;
-  return p;
+__device__ __forceinline__ int chunk_tiles(int cs, int L) {
+  const int left = (L - cs * TL) >> 4;
+  return left < TL / 16 ? left : TL / 16;
 }
 
-// Turns the raw coefficients of a chunk (already in shared memory at `tbuf`) into per-block
-// inclusive prefix sums of log2 a, in place.  Lane l owns tokens 4l..4l+3; four lanes = one block.
-template <int COEF, int TL>
-__device__ __forceinline__ void coeff_to_prefix(float* tbuf, int lane) {
-  constexpr int kLanes = TL / 4;
-  const int l = (kLanes == 32) ? lane : (lane & (kLanes - 1));
-  float v0, v1, v2, v3;
+// Once per chunk: raw coefficients (already in shared memory at tab[0..]) -> per-token tables.
+// Lane l owns TPL = TL/32 consecutive tokens; 16/TPL lanes make one block; the prefix sums restart
+// at every block.  Tables (each TL floats): [0] T, then forward [1] P = 2^T,
+// backward [1] Pshift (P of the previous token, 1 for the first token of a block), [2] L15 = 2^(T_15 - T).
+template <int COEF, int TL, bool BWD>
+__device__ __forceinline__ void chunk_tables(float* tab, int lane) {
+  constexpr int TPL = TL / 32;    // tokens per lane: 2 or 4
+  constexpr int LPT = 16 / TPL;   // lanes per block: 8 or 4
+  float v[TPL];
   if constexpr (COEF == kCoefBf16) {
-    const uint2 raw = reinterpret_cast<const uint2*>(tbuf)[l];
-    v0 = bf16_lo(raw.x); v1 = bf16_hi(raw.x); v2 = bf16_lo(raw.y); v3 = bf16_hi(raw.y);
+    if constexpr (TPL == 4) {
+      const uint2 raw = reinterpret_cast<const uint2*>(tab)[lane];
+      v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
+    } else {
+      const uint32_t raw = reinterpret_cast<const uint32_t*>(tab)[lane];
+      v[0] = bf16_lo(raw); v[1] = bf16_hi(raw);
+    }
   } else {
-    const float4 raw = reinterpret_cast<const float4*>(tbuf)[l];
-    v0 = raw.x; v1 = raw.y; v2 = raw.z; v3 = raw.w;
+    if constexpr (TPL == 4) {
+      const float4 raw = reinterpret_cast<const float4*>(tab)[lane];
+      v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+    } else {
+      const float2 raw = reinterpret_cast<const float2*>(tab)[lane];
+      v[0] = raw.x; v[1] = raw.y;
+    }
   }
-  const float s0 = coef_log2<COEF>(v0);
-  const float s1 = s0 + coef_log2<COEF>(v1);
-  const float s2 = s1 + coef_log2<COEF>(v2);
-  const float s3 = s2 + coef_log2<COEF>(v3);
-  const float u1 = __shfl_up_sync(0xffffffffu, s3, 1, 4);
-  const float u2 = __shfl_up_sync(0xffffffffu, s3, 2, 4);
-  const float u3 = __shfl_up_sync(0xffffffffu, s3, 3, 4);
-  const int q = lane & 3;
-  float e = 0.0f;
-  if (q >= 1) e += u1;
-  if (q >= 2) e += u2;
-  if (q >= 3) e += u3;
+  float T[TPL];
+  T[0] = coef_log2<COEF>(v[0]);
+#pragma unroll
+  for (int k = 1; k < TPL; ++k) T[k] = T[k - 1] + coef_log2<COEF>(v[k]);
+  // exclusive prefix of the lane totals inside the block
+  const int q = lane & (LPT - 1);
+  float inc = T[TPL - 1];
+#pragma unroll
+  for (int d = 1; d < LPT; d <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, inc, d, LPT);
+    if (q >= d) inc += up;
+  }
+  float excl = __shfl_up_sync(0xffffffffu, inc, 1, LPT);
+  if (q == 0) excl = 0.0f;
+  float P[TPL];
+#pragma unroll
+  for (int k = 0; k < TPL; ++k) {
+    T[k] += excl;
+    P[k] = ex2(T[k]);
+  }
+  float second[TPL], third[TPL];
+  if constexpr (BWD) {
+    const float T15 = __shfl_sync(0xffffffffu, T[TPL - 1], lane | (LPT - 1));
+    float prev = __shfl_up_sync(0xffffffffu, P[TPL - 1], 1, LPT);
+    if (q == 0) prev = 1.0f;
+    second[0] = prev;
+#pragma unroll
+    for (int k = 1; k < TPL; ++k) second[k] = P[k - 1];
+#pragma unroll
+    for (int k = 0; k < TPL; ++k) third[k] = ex2(T15 - T[k]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < TPL; ++k) {
+      second[k] = P[k];
+      third[k] = 0.0f;
+    }
+  }
   __syncwarp();  // every lane has read its raw coefficients
-  if (kLanes == 32 || lane < kLanes) {
-    reinterpret_cast<float4*>(tbuf)[l] = make_float4(s0 + e, s1 + e, s2 + e, s3 + e);
+  if constexpr (TPL == 4) {
+    reinterpret_cast<float4*>(tab)[lane] = make_float4(T[0], T[1], T[2], T[3]);
+    reinterpret_cast<float4*>(tab + TL)[lane] = make_float4(second[0], second[1], second[2], second[3]);
+    if constexpr (BWD) reinterpret_cast<float4*>(tab + 2 * TL)[lane] = make_float4(third[0], third[1], third[2], third[3]);
+  } else {
+    reinterpret_cast<float2*>(tab)[lane] = make_float2(T[0], T[1]);
+    reinterpret_cast<float2*>(tab + TL)[lane] = make_float2(second[0], second[1]);
+    if constexpr (BWD) reinterpret_cast<float2*>(tab + 2 * TL)[lane] = make_float2(third[0], third[1]);
   }
   __syncwarp();
 }
@@ -239,30 +283,30 @@ __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* c
   out_g8 = sg8;
 }
 
-// Lane-constant indexing of a 16x16 bf16 tile inside a 128-byte-swizzled [16][64] box.
+// Lane-constant pieces of the addressing of 16x16 bf16 blocks inside 128-byte-swizzled [16][64] boxes.
+// Block ib (0..3) of a box occupies the 16-byte columns 2*ib and 2*ib+1 of every 128-byte row; the
+// hardware swizzle stores column c of row r at column c ^ (r & 7).
 struct TileLane {
   int g, t;
-  uint32_t ldm_row_off;  // ldmatrix: byte offset of this lane's row
-  uint32_t ldm_rx;       // ldmatrix: row & 7 (swizzle key)
-  uint32_t ldm_hsel;     // ldmatrix: which 8-token half this lane addresses
-  bool m0, m1;           // 2t <= g, 2t+1 <= g  (causal mask of the fragment elements)
+  uint32_t ldm_base;    // ldmatrix: byte offset of this lane's row
+  uint32_t ldm_off[4];  // ldmatrix: swizzled column offset for ib = 0..3
+  uint32_t st_base;     // fragment store: byte offset of (channel g, tokens 2t..2t+1)
+  uint32_t st_off[4];   // fragment store: swizzled column offset of the first token half, ib = 0..3
+  bool m0, m1;          // 2t <= g, 2t+1 <= g  (causal mask of the fragment elements)
   __device__ __forceinline__ explicit TileLane(int lane) {
     g = lane >> 2;
     t = lane & 3;
     const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
-    ldm_row_off = row * 128;
-    ldm_rx = row & 7;
-    ldm_hsel = lane >> 4;
+    const uint32_t key = (lane >> 4) ^ (row & 7);
+    ldm_base = row * 128;
+    st_base = g * 128 + t * 4;
+#pragma unroll
+    for (int ib = 0; ib < 4; ++ib) {
+      ldm_off[ib] = ((2u * ib) ^ key) << 4;
+      st_off[ib] = ((2u * ib) ^ static_cast<uint32_t>(g)) << 4;
+    }
     m0 = (2 * t) <= g;
     m1 = (2 * t + 1) <= g;
-  }
-  // address for ldmatrix.x4 of block i (0..3 inside its box) -> A fragment (channels x tokens)
-  __device__ __forceinline__ uint32_t ldm_addr(uint32_t box_base, int ib) const {
-    return box_base + ldm_row_off + (((ib * 2 + ldm_hsel) ^ ldm_rx) << 4);
-  }
-  // address of the 4 bytes (channel g, tokens 2t..2t+1) of token-half `half` of block ib; channel g+8 is +1024
-  __device__ __forceinline__ uint32_t frag_addr(uint32_t box_base, int ib, int half) const {
-    return box_base + g * 128 + (((ib * 2 + half) ^ g) << 4) + t * 4;
   }
 };
 
@@ -273,11 +317,12 @@ struct LmatFrag {
   uint32_t b11;  // rows 8..15 x cols 8..15
 };
 
-__device__ __forceinline__ LmatFrag build_lmat(const float* Tt, const TileLane& tl, float2& Ta, float2& Tb) {
-  const float Tg = Tt[tl.g];
-  const float Tg8 = Tt[tl.g + 8];
-  Ta = *reinterpret_cast<const float2*>(Tt + 2 * tl.t);
-  Tb = *reinterpret_cast<const float2*>(Tt + 8 + 2 * tl.t);
+// tg = &T[g], tt = &T[2t] of the chunk; `off` = 16 * block index (a compile-time constant in the hot loops)
+__device__ __forceinline__ LmatFrag build_lmat(const float* tg, const float* tt, int off, const TileLane& tl) {
+  const float Tg = tg[off];
+  const float Tg8 = tg[off + 8];
+  const float2 Ta = *reinterpret_cast<const float2*>(tt + off);
+  const float2 Tb = *reinterpret_cast<const float2*>(tt + off + 8);
   const float e0 = tl.m0 ? ex2(Tg - Ta.x) : 0.0f;
   const float e1 = tl.m1 ? ex2(Tg - Ta.y) : 0.0f;
   const float e2 = ex2(Tg8 - Ta.x);
@@ -308,6 +353,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    const KernelParams p) {
   using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, false, false>;
   constexpr int TL = LAYOUT::kTL;
+  constexpr int NT = LAYOUT::kTiles;
   constexpr int kEsz = CoefTraits<COEF>::kBytes;
   // Loads run AHEAD chunks in front of the one being computed.  A bf16 output leaves through the
   // stage buffer itself, so a stage is reloaded only two chunks after its store was issued.
@@ -317,7 +363,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   extern __shared__ unsigned char smem_raw[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const WarpSmem<LAYOUT, STAGES> ws = carve_smem<LAYOUT, STAGES, WARPS>(smem_raw, warp);
+  const WarpSmem<LAYOUT> ws = carve_smem<LAYOUT, STAGES>(smem_raw, warp);
   const TileLane tl(lane);
 
   // contiguous range of chunks for this warp
@@ -338,113 +384,143 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   }
   __syncwarp();
 
-  auto issue = [&](int j) {  // lane 0: start the loads of local chunk j into its stage
-    const ChunkPos c = chunk_pos<TL>(cb + j, p.ncs, p.L);
-    const int s = j % STAGES;
-    const int nbox = (c.nt + 3) >> 2;
-    const uint32_t cbytes = c.nt * 16 * kEsz;
-    mbar_arrive_expect_tx(ws.bar(s), nbox * 2048 + cbytes);
-    for (int b = 0; b < nbox; ++b) tma_load_2d(ws.x(s) + b * 2048, &tm_x, c.c0 + 64 * b, c.bh * 16, ws.bar(s));
-    bulk_load(ws.t_addr(s), reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(c.bh) * p.L + c.c0) * kEsz,
-              cbytes, ws.bar(s));
+  const int L = p.L, ncs = p.ncs;
+  ChunkCursor prod(cb, ncs), cons(cb, ncs);
+  int s_prod = 0;
+  auto issue = [&]() {  // starts the loads of the producer cursor's chunk into stage s_prod, then advances
+    if (lane == 0) {
+      const int nt = chunk_tiles<TL>(prod.cs, L);
+      const int c0 = prod.cs * TL;
+      const int nbox = (nt + 3) >> 2;
+      const uint32_t cbytes = nt * 16 * kEsz;
+      const uint32_t bar = ws.bar(s_prod);
+      mbar_arrive_expect_tx(bar, nbox * 2048 + cbytes);
+#pragma unroll
+      for (int b = 0; b < NBOX; ++b)
+        if (b < nbox) tma_load_2d(ws.x(s_prod) + b * 2048, &tm_x, c0 + 64 * b, prod.bh * 16, bar);
+      bulk_load(ws.tab_addr(s_prod),
+                reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(prod.bh) * L + c0) * kEsz, cbytes, bar);
+    }
+    prod.next(ncs);
+    s_prod = (s_prod + 1 == STAGES) ? 0 : s_prod + 1;
   };
 
-  if (lane == 0) {
-    for (int j = 0; j < AHEAD && j < n; ++j) issue(j);
-  }
+  for (int k = 0; k < AHEAD && k < n; ++k) issue();
 
   float cg = 0.0f, cg8 = 0.0f;  // carry into the next block, channels g and g+8
   bool failed = false;
-  int pending_from = 0;  // first local chunk whose load may still be in flight (for the failure path)
+  int j = 0, s = 0;
+  uint32_t phase = 0;
 
-  for (int j = 0; j < n; ++j) {
-    const int s = j % STAGES;
-    const ChunkPos c = chunk_pos<TL>(cb + j, p.ncs, p.L);
-    if (lane == 0 && j + AHEAD < n) {
-      if (!OUT_F32) bulk_wait_group_read<1>();  // the store that last used that stage has drained
-      issue(j + AHEAD);
+  for (; j < n; ++j) {
+    if (j + AHEAD < n) {
+      if (!OUT_F32 && lane == 0) bulk_wait_group_read<1>();  // the store that last used that stage has drained
+      issue();
     }
-    pending_from = j;
-    if (!mbar_wait_bounded(ws.bar(s), (j / STAGES) & 1, kWaitLimitNs)) {
+    if (!mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs)) {
       failed = true;
       break;
     }
-    pending_from = j + 1;
-    float* T = ws.t_ptr(s);
-    coeff_to_prefix<COEF, TL>(T, lane);
+    const int nt = chunk_tiles<TL>(cons.cs, L);
+    const int c0 = cons.cs * TL;
+    float* tab = ws.tab_ptr(s);
+    chunk_tables<COEF, TL, false>(tab, lane);
 
-    if (c.cs == 0 || !p.use_carry) {
+    if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
     } else if (j == 0) {
-      halo_reduce<COEF, false, false>(p.x, p.coeff, p.L, c.bh, c.c0 - 16, lane, cg, cg8);
+      halo_reduce<COEF, false, false>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
     }
 
-    for (int i = 0; i < c.nt; ++i) {
-      const int box = i >> 2, ib = i & 3;
-      const uint32_t box_base = ws.x(s) + box * 2048;
-      float2 Ta, Tb;
-      const LmatFrag lf = build_lmat(T + 16 * i, tl, Ta, Tb);
-      uint32_t a0, a1, a2, a3;
-      ldmatrix_x4(tl.ldm_addr(box_base, ib), a0, a1, a2, a3);
-      float v0[4], v1[4];
-      mma_1688(v0, a0, a1, lf.b00);
-      mma_16816(v1, a0, a1, a2, a3, lf.b10, lf.b11);
-      const float p0 = ex2(Ta.x), p1 = ex2(Ta.y), p2 = ex2(Tb.x), p3 = ex2(Tb.y);
-      float y0[4], y1[4];
-      y0[0] = fmaf(p0, cg, v0[0]);  y0[1] = fmaf(p1, cg, v0[1]);
-      y0[2] = fmaf(p0, cg8, v0[2]); y0[3] = fmaf(p1, cg8, v0[3]);
-      y1[0] = fmaf(p2, cg, v1[0]);  y1[1] = fmaf(p3, cg, v1[1]);
-      y1[2] = fmaf(p2, cg8, v1[2]); y1[3] = fmaf(p3, cg8, v1[3]);
-      // carry for the next block: the UNCORRECTED last token (btp-forward.cu:297-299)
-      const int src = lane | 3;
-      const float ng = __shfl_sync(0xffffffffu, v1[1], src);
-      const float ng8 = __shfl_sync(0xffffffffu, v1[3], src);
-      if constexpr (CKPT) {
-        const int tile_in_seq = c.cs * (TL / 16) + i;
-        const int tiles_per_seq = p.L >> 4;
-        if (p.use_carry && tl.t == 3 && tile_in_seq < tiles_per_seq - 1) {
-          float* dst = p.ckpt + (static_cast<long long>(c.bh) * tiles_per_seq + tile_in_seq) * 16;
-          dst[tl.g] = v1[1];
-          dst[tl.g + 8] = v1[3];
+    const float* tg = tab + tl.g;
+    const float* tt = tab + 2 * tl.t;
+    const uint32_t xs = ws.x(s);
+    const uint32_t ldm = xs + tl.ldm_base;
+    const uint32_t stb = xs + tl.st_base;
+    float* yo = nullptr;
+    if constexpr (OUT_F32) {
+      yo = reinterpret_cast<float*>(p.out_f32) + (static_cast<long long>(cons.bh) * 16 + tl.g) * L + c0 + 2 * tl.t;
+    }
+    float* ck = nullptr;
+    if constexpr (CKPT) {
+      ck = p.ckpt + (static_cast<long long>(cons.bh) * (L >> 4) + cons.cs * NT) * 16 + tl.g;
+    }
+
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      if (i < nt) {
+        const int box = i >> 2, ib = i & 3;
+        const LmatFrag lf = build_lmat(tg, tt, 16 * i, tl);
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(ldm + box * 2048 + tl.ldm_off[ib], a0, a1, a2, a3);
+        float v0[4], v1[4];
+        mma_1688(v0, a0, a1, lf.b00);
+        mma_16816(v1, a0, a1, a2, a3, lf.b10, lf.b11);
+        const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
+        const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);
+        float y0[4], y1[4];
+        y0[0] = fmaf(Pa.x, cg, v0[0]);  y0[1] = fmaf(Pa.y, cg, v0[1]);
+        y0[2] = fmaf(Pa.x, cg8, v0[2]); y0[3] = fmaf(Pa.y, cg8, v0[3]);
+        y1[0] = fmaf(Pb.x, cg, v1[0]);  y1[1] = fmaf(Pb.y, cg, v1[1]);
+        y1[2] = fmaf(Pb.x, cg8, v1[2]); y1[3] = fmaf(Pb.y, cg8, v1[3]);
+        if constexpr (CKPT) {
+          // slot j of the checkpoint = block-local last token of block j, except the last block
+          if (p.use_carry && tl.t == 3 && (cons.cs * NT + i) < (L >> 4) - 1) {
+            ck[16 * i] = v1[1];
+            ck[16 * i + 8] = v1[3];
+          }
         }
-      }
-      if (p.use_carry) { cg = ng; cg8 = ng8; }
-      if constexpr (OUT_F32) {
-        float* yo = reinterpret_cast<float*>(p.out_f32) +
-                    (static_cast<long long>(c.bh) * 16 + tl.g) * p.L + c.c0 + 16 * i + 2 * tl.t;
-        const long long r8 = 8ll * p.L;
-        *reinterpret_cast<float2*>(yo) = make_float2(y0[0], y0[1]);
-        *reinterpret_cast<float2*>(yo + r8) = make_float2(y0[2], y0[3]);
-        *reinterpret_cast<float2*>(yo + 8) = make_float2(y1[0], y1[1]);
-        *reinterpret_cast<float2*>(yo + r8 + 8) = make_float2(y1[2], y1[3]);
-      } else {
-        __syncwarp();  // all lanes have consumed this block's x before it is overwritten
-        const uint32_t o0 = tl.frag_addr(box_base, ib, 0);
-        const uint32_t o1 = tl.frag_addr(box_base, ib, 1);
-        st_shared_u32(o0, pack_bf16x2(y0[0], y0[1]));
-        st_shared_u32(o0 + 1024, pack_bf16x2(y0[2], y0[3]));
-        st_shared_u32(o1, pack_bf16x2(y1[0], y1[1]));
-        st_shared_u32(o1 + 1024, pack_bf16x2(y1[2], y1[3]));
+        if (p.use_carry) {
+          // carry for the next block: the UNCORRECTED last token (btp-forward.cu:297-299)
+          cg = __shfl_sync(0xffffffffu, v1[1], lane | 3);
+          cg8 = __shfl_sync(0xffffffffu, v1[3], lane | 3);
+        }
+        if constexpr (OUT_F32) {
+          const long long r8 = 8ll * L;
+          *reinterpret_cast<float2*>(yo + 16 * i) = make_float2(y0[0], y0[1]);
+          *reinterpret_cast<float2*>(yo + 16 * i + r8) = make_float2(y0[2], y0[3]);
+          *reinterpret_cast<float2*>(yo + 16 * i + 8) = make_float2(y1[0], y1[1]);
+          *reinterpret_cast<float2*>(yo + 16 * i + 8 + r8) = make_float2(y1[2], y1[3]);
+        } else {
+          __syncwarp();  // all lanes have consumed this block's x before it is overwritten
+          const uint32_t o0 = stb + box * 2048 + tl.st_off[ib];
+          const uint32_t o1 = o0 ^ 16u;
+          st_shared_u32(o0, pack_bf16x2(y0[0], y0[1]));
+          st_shared_u32(o0 + 1024, pack_bf16x2(y0[2], y0[3]));
+          st_shared_u32(o1, pack_bf16x2(y1[0], y1[1]));
+          st_shared_u32(o1 + 1024, pack_bf16x2(y1[2], y1[3]));
+        }
       }
     }
     if constexpr (!OUT_F32) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        const int nbox = (c.nt + 3) >> 2;
-        for (int b = 0; b < nbox; ++b) tma_store_2d(&tm_y, c.c0 + 64 * b, c.bh * 16, ws.x(s) + b * 2048);
+        const int nbox = (nt + 3) >> 2;
+#pragma unroll
+        for (int b = 0; b < NBOX; ++b)
+          if (b < nbox) tma_store_2d(&tm_y, c0 + 64 * b, cons.bh * 16, xs + b * 2048);
         bulk_commit_group();
       }
     } else {
-      __syncwarp();  // T of this stage is free again
+      __syncwarp();  // the tables of this stage are free again
+    }
+    cons.next(ncs);
+    if (++s == STAGES) {
+      s = 0;
+      phase ^= 1u;
     }
   }
 
   if (failed) {
-    if (lane == 0) report_timeout(warp, cb + pending_from);
+    if (lane == 0) report_timeout(warp, cb + j);
     // give the loads still in flight a (bounded) chance to land before the buffers are released
-    for (int j = pending_from; j < n && j < pending_from + AHEAD + 1; ++j) {
-      mbar_wait_bounded(ws.bar(j % STAGES), (j / STAGES) & 1, kWaitLimitNs);
+    for (int k = j; k < n && k <= j + AHEAD; ++k) {
+      mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs);
+      if (++s == STAGES) {
+        s = 0;
+        phase ^= 1u;
+      }
     }
   }
   if (!OUT_F32 && lane == 0) bulk_wait_group<0>();
@@ -458,28 +534,20 @@ struct TileAcc {
   float g0[4], g1[4];  // gw = dy . Lmat
 };
 
-struct PendingTile {
-  int stage;
-  int i;            // block inside its chunk
-  float cg, cg8;    // carry INTO this block
-  bool seq_end;     // last block of its sequence: no gradient arrives from the right
-  bool chunk_end;   // last block of its chunk: outputs of the chunk are complete after it
-  int bh, c0, nt;   // chunk coordinates, for the stores
-};
-
 template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                     const __grid_constant__ CUtensorMap tm_dx, const KernelParams p) {
   using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, true, DY_F32>;
   constexpr int TL = LAYOUT::kTL;
+  constexpr int NT = LAYOUT::kTiles;
   constexpr int kEsz = CoefTraits<COEF>::kBytes;
   static_assert(STAGES >= 3, "the backward ring needs three stages");
 
   extern __shared__ unsigned char smem_raw[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const WarpSmem<LAYOUT, STAGES> ws = carve_smem<LAYOUT, STAGES, WARPS>(smem_raw, warp);
+  const WarpSmem<LAYOUT> ws = carve_smem<LAYOUT, STAGES>(smem_raw, warp);
   const TileLane tl(lane);
 
   const long long nwarps = static_cast<long long>(gridDim.x) * WARPS;
@@ -500,84 +568,89 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   }
   __syncwarp();
 
-  auto issue = [&](int j) {
-    const ChunkPos c = chunk_pos<TL>(cb + j, p.ncs, p.L);
-    const int s = j % STAGES;
-    const int nbox = (c.nt + 3) >> 2;
-    const int nbox_dy = DY_F32 ? (c.nt + 1) >> 1 : nbox;
-    const uint32_t cbytes = c.nt * 16 * kEsz;
-    mbar_arrive_expect_tx(ws.bar(s), (nbox + nbox_dy) * 2048 + cbytes);
-    for (int b = 0; b < nbox; ++b) tma_load_2d(ws.x(s) + b * 2048, &tm_x, c.c0 + 64 * b, c.bh * 16, ws.bar(s));
-    for (int b = 0; b < nbox_dy; ++b)
-      tma_load_2d(ws.dy(s) + b * 2048, &tm_dy, c.c0 + (DY_F32 ? 32 : 64) * b, c.bh * 16, ws.bar(s));
-    bulk_load(ws.t_addr(s), reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(c.bh) * p.L + c.c0) * kEsz,
-              cbytes, ws.bar(s));
+  const int L = p.L, ncs = p.ncs;
+  ChunkCursor prod(cb, ncs), cons(cb, ncs);
+  int s_prod = 0, issued = 0;
+  auto issue = [&]() {
+    if (lane == 0) {
+      const int nt = chunk_tiles<TL>(prod.cs, L);
+      const int c0 = prod.cs * TL;
+      const int nbox = (nt + 3) >> 2;
+      const int nbox_dy = DY_F32 ? (nt + 1) >> 1 : nbox;
+      const uint32_t cbytes = nt * 16 * kEsz;
+      const uint32_t bar = ws.bar(s_prod);
+      mbar_arrive_expect_tx(bar, (nbox + nbox_dy) * 2048 + cbytes);
+#pragma unroll
+      for (int b = 0; b < NBOX; ++b)
+        if (b < nbox) tma_load_2d(ws.x(s_prod) + b * 2048, &tm_x, c0 + 64 * b, prod.bh * 16, bar);
+#pragma unroll
+      for (int b = 0; b < (DY_F32 ? 2 * NBOX : NBOX); ++b)
+        if (b < nbox_dy) tma_load_2d(ws.dy(s_prod) + b * 2048, &tm_dy, c0 + (DY_F32 ? 32 : 64) * b, prod.bh * 16, bar);
+      bulk_load(ws.tab_addr(s_prod),
+                reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(prod.bh) * L + c0) * kEsz, cbytes, bar);
+    }
+    prod.next(ncs);
+    s_prod = (s_prod + 1 == STAGES) ? 0 : s_prod + 1;
+    ++issued;
   };
 
   // Chunk j's outputs leave one block into chunk j+1 (its last block needs the gradient that
-  // arrives from the right).  Stage of chunk j is reloaded with chunk j+STAGES one chunk later
-  // still, when that store has certainly drained: loads run STAGES-2 chunks ahead.
-  int issued = 0;  // uniform across the warp; only lane 0 acts on it
-  for (; issued < STAGES - 1 && issued < n; ++issued) {
-    if (lane == 0) issue(issued);
-  }
+  // arrives from the right).  The stage of chunk j is reloaded one chunk later still, when that
+  // store has certainly drained: loads run STAGES-2 chunks ahead.
+  while (issued < STAGES - 1 && issued < n) issue();
 
-  // Front half of a block: tensor-core products.  Back half: everything that needs dCarry.
-  auto front = [&](int s, int i, TileAcc& acc, float& dc_g, float& dc_g8) {
+  // ---- front half of a block: Lmat fragments and the four tensor-core products
+  auto front = [&](const float* tab, const float* tg, const float* tt, uint32_t ldm_x, uint32_t dy_s, int i,
+                   TileAcc& acc, float& dc_g, float& dc_g8) {
     const int box = i >> 2, ib = i & 3;
-    const float* Tt = ws.t_ptr(s) + 16 * i;
-    float2 Ta, Tb;
-    const LmatFrag lf = build_lmat(Tt, tl, Ta, Tb);
+    const LmatFrag lf = build_lmat(tg, tt, 16 * i, tl);
     // dy . Lmat needs the transposed 8x8 blocks as B operand (k = r, n = c)
     const uint32_t g00 = movmatrix_trans(lf.b00);
     const uint32_t g10 = movmatrix_trans(lf.b10);
     const uint32_t g11 = movmatrix_trans(lf.b11);
     uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-    ldmatrix_x4(tl.ldm_addr(ws.x(s) + box * 2048, ib), a0, a1, a2, a3);
+    ldmatrix_x4(ldm_x + box * 2048 + tl.ldm_off[ib], a0, a1, a2, a3);
     if constexpr (DY_F32) {
-      // [16][32] float boxes, 128-byte swizzle: block i sits in box i/2 at 64-byte offset (i&1)*64
-      const uint32_t bb = ws.dy(s) + (i >> 1) * 2048 + tl.g * 128;
+      // [16][32] float boxes, 128-byte swizzle: block i sits in box i/2 at byte offset (i&1)*64 of each row
+      const uint32_t bb = dy_s + (i >> 1) * 2048 + tl.g * 128;
       const uint32_t c_lo = ((i & 1) * 4 + (tl.t >> 1)), c_hi = c_lo + 2;
       const uint32_t in = (tl.t & 1) * 8;
-      float2 f;
       auto lds = [&](uint32_t addr) {
         float2 r;
         asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(r.x), "=f"(r.y) : "r"(addr));
         return r;
       };
+      float2 f;
       f = lds(bb + ((c_lo ^ tl.g) << 4) + in);         e0 = pack_bf16x2(f.x, f.y);
       f = lds(bb + 1024 + ((c_lo ^ tl.g) << 4) + in);  e1 = pack_bf16x2(f.x, f.y);
       f = lds(bb + ((c_hi ^ tl.g) << 4) + in);         e2 = pack_bf16x2(f.x, f.y);
       f = lds(bb + 1024 + ((c_hi ^ tl.g) << 4) + in);  e3 = pack_bf16x2(f.x, f.y);
     } else {
-      ldmatrix_x4(tl.ldm_addr(ws.dy(s) + box * 2048, ib), e0, e1, e2, e3);
+      ldmatrix_x4(ldm_x + LAYOUT::kXBytes + box * 2048 + tl.ldm_off[ib], e0, e1, e2, e3);
     }
     mma_1688(acc.v0, a0, a1, lf.b00);
     mma_16816(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
     mma_16816(acc.g0, e0, e1, e2, e3, g00, g10);
     mma_1688(acc.g1, e2, e3, g11);
-    // gradient this block sends to its left neighbour: a_0 * gw[:,0]
-    const float a_first = ex2(Tt[0]);
-    const int src = lane & ~3;
-    dc_g = a_first * __shfl_sync(0xffffffffu, acc.g0[0], src);
-    dc_g8 = a_first * __shfl_sync(0xffffffffu, acc.g0[2], src);
+    // gradient this block sends to its left neighbour: P[0] * gw[:,0]   (P[0] = Pshift[1])
+    const float a_first = tab[TL + 16 * i + 1];
+    dc_g = a_first * __shfl_sync(0xffffffffu, acc.g0[0], lane & ~3);
+    dc_g8 = a_first * __shfl_sync(0xffffffffu, acc.g0[2], lane & ~3);
   };
 
-  auto back = [&](const PendingTile& pt, const TileAcc& acc, float dc_g, float dc_g8) {
-    const int s = pt.stage, i = pt.i;
-    const int box = i >> 2, ib = i & 3;
-    const float* Tt = ws.t_ptr(s) + 16 * i;
-    const float2 Ta = *reinterpret_cast<const float2*>(Tt + 2 * tl.t);
-    const float2 Tb = *reinterpret_cast<const float2*>(Tt + 8 + 2 * tl.t);
-    const float T15 = Tt[15];
-    const float Tm1 = tl.t ? Tt[2 * tl.t - 1] : 0.0f;  // P[-1] = 1
-    const float T7 = Tt[2 * tl.t + 7];
-    const float l0 = ex2(T15 - Ta.x), l1 = ex2(T15 - Ta.y), l2 = ex2(T15 - Tb.x), l3 = ex2(T15 - Tb.y);
+  // ---- back half of a block: everything that needs the gradient arriving from the right.
+  // tt_i = &T[16 i + 2t] of the block's chunk, da_i = &dA_stage[16 i], o0 = dx store address.
+  auto back = [&](const TileAcc& acc, const float* tt_i, float* da_i, uint32_t o0, float cg, float cg8, float dc_g,
+                  float dc_g8) {
+    const float2 Sa = *reinterpret_cast<const float2*>(tt_i + TL);          // P[2t-1], P[2t]
+    const float2 Sb = *reinterpret_cast<const float2*>(tt_i + TL + 8);      // P[2t+7], P[2t+8]
+    const float2 La = *reinterpret_cast<const float2*>(tt_i + 2 * TL);      // Lmat[15, 2t], Lmat[15, 2t+1]
+    const float2 Lb = *reinterpret_cast<const float2*>(tt_i + 2 * TL + 8);  // Lmat[15, 2t+8], Lmat[15, 2t+9]
     float dx0[4], dx1[4];
-    dx0[0] = fmaf(l0, dc_g, acc.g0[0]);  dx0[1] = fmaf(l1, dc_g, acc.g0[1]);
-    dx0[2] = fmaf(l0, dc_g8, acc.g0[2]); dx0[3] = fmaf(l1, dc_g8, acc.g0[3]);
-    dx1[0] = fmaf(l2, dc_g, acc.g1[0]);  dx1[1] = fmaf(l3, dc_g, acc.g1[1]);
-    dx1[2] = fmaf(l2, dc_g8, acc.g1[2]); dx1[3] = fmaf(l3, dc_g8, acc.g1[3]);
+    dx0[0] = fmaf(La.x, dc_g, acc.g0[0]);  dx0[1] = fmaf(La.y, dc_g, acc.g0[1]);
+    dx0[2] = fmaf(La.x, dc_g8, acc.g0[2]); dx0[3] = fmaf(La.y, dc_g8, acc.g0[3]);
+    dx1[0] = fmaf(Lb.x, dc_g, acc.g1[0]);  dx1[1] = fmaf(Lb.y, dc_g, acc.g1[1]);
+    dx1[2] = fmaf(Lb.x, dc_g8, acc.g1[2]); dx1[3] = fmaf(Lb.y, dc_g8, acc.g1[3]);
     // v shifted right by one token
     const int src = (lane & ~3) | ((lane + 3) & 3);
     const float A_g = __shfl_sync(0xffffffffu, acc.v0[1], src);
@@ -586,16 +659,14 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const float B_g8 = __shfl_sync(0xffffffffu, acc.v1[3], src);
     const float vp0_g = tl.t ? A_g : 0.0f, vp0_g8 = tl.t ? A_g8 : 0.0f;
     const float vp2_g = tl.t ? B_g : A_g, vp2_g8 = tl.t ? B_g8 : A_g8;
-    const float pc0 = ex2(Tm1), pc1 = ex2(Ta.x), pc2 = ex2(T7), pc3 = ex2(Tb.x);
-    const float cg = pt.cg, cg8 = pt.cg8;
     float m0 = fmaf(vp0_g, dx0[0], vp0_g8 * dx0[2]);
     float m1 = fmaf(acc.v0[0], dx0[1], acc.v0[2] * dx0[3]);
     float m2 = fmaf(vp2_g, dx1[0], vp2_g8 * dx1[2]);
     float m3 = fmaf(acc.v1[0], dx1[1], acc.v1[2] * dx1[3]);
-    m0 = fmaf(pc0, fmaf(acc.g0[0], cg, acc.g0[2] * cg8), m0);
-    m1 = fmaf(pc1, fmaf(acc.g0[1], cg, acc.g0[3] * cg8), m1);
-    m2 = fmaf(pc2, fmaf(acc.g1[0], cg, acc.g1[2] * cg8), m2);
-    m3 = fmaf(pc3, fmaf(acc.g1[1], cg, acc.g1[3] * cg8), m3);
+    m0 = fmaf(Sa.x, fmaf(acc.g0[0], cg, acc.g0[2] * cg8), m0);
+    m1 = fmaf(Sa.y, fmaf(acc.g0[1], cg, acc.g0[3] * cg8), m1);
+    m2 = fmaf(Sb.x, fmaf(acc.g1[0], cg, acc.g1[2] * cg8), m2);
+    m3 = fmaf(Sb.y, fmaf(acc.g1[1], cg, acc.g1[3] * cg8), m3);
     // sum over the 16 channels: channel pairs are in-thread, the 8 groups g are folded by a
     // transposing butterfly (each step halves the number of tokens a lane keeps)
     const bool b0 = (tl.g & 1) != 0, b1 = (tl.g & 2) != 0;
@@ -609,99 +680,132 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     if (lane < 16) {
       // token kept by this lane: [2t, 2t+1, 2t+8, 2t+9][2*b0 + b1]
       const int tok = 2 * tl.t + (b1 ? 1 : 0) + (b0 ? 8 : 0);
-      float val = r;
       if constexpr (COEF == kCoefF32Log) {
-        // gradient w.r.t. the log coefficient: dA * a,  a_tok = 2^(T_tok - T_{tok-1})
+        // gradient w.r.t. the log coefficient: dA * a,  a_tok = P[tok] / P[tok-1] = 2^(T_tok - T_{tok-1})
+        const float* Tt = tt_i - 2 * tl.t;
         const float Tprev = tok ? Tt[tok - 1] : 0.0f;
-        val *= ex2(Tt[tok] - Tprev);
+        r *= ex2(Tt[tok] - Tprev);
       }
-      ws.da_ptr(s)[16 * i + tok] = val;
+      da_i[tok] = r;
     }
     // dx replaces the consumed x block in shared memory
-    const uint32_t box_base = ws.x(s) + box * 2048;
-    const uint32_t o0 = tl.frag_addr(box_base, ib, 0);
-    const uint32_t o1 = tl.frag_addr(box_base, ib, 1);
+    const uint32_t o1 = o0 ^ 16u;
     st_shared_u32(o0, pack_bf16x2(dx0[0], dx0[1]));
     st_shared_u32(o0 + 1024, pack_bf16x2(dx0[2], dx0[3]));
     st_shared_u32(o1, pack_bf16x2(dx1[0], dx1[1]));
     st_shared_u32(o1 + 1024, pack_bf16x2(dx1[2], dx1[3]));
   };
 
-  auto flush = [&](const PendingTile& pt) {  // chunk complete: send dx and dA on their way
+  // pending block = last block of the previous chunk; its accumulators live in slot B
+  TileAcc accA, accB;
+  bool have = false, failed = false;
+  bool p_seq_end = false;
+  const float* p_tt = nullptr;
+  float* p_da = nullptr;
+  uint32_t p_o0 = 0;
+  float p_cg = 0.0f, p_cg8 = 0.0f;
+  int p_stage = 0, p_bh = 0, p_c0 = 0, p_nt = 0;
+  float vl_g = 0.0f, vl_g8 = 0.0f;  // uncorrected last token of the most recent block
+
+  auto flush = [&]() {  // the pending block's chunk is complete: send dx and dA on their way
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      const int nbox = (pt.nt + 3) >> 2;
-      for (int b = 0; b < nbox; ++b) tma_store_2d(&tm_dx, pt.c0 + 64 * b, pt.bh * 16, ws.x(pt.stage) + b * 2048);
-      bulk_store(p.dA + static_cast<long long>(pt.bh) * p.L + pt.c0, ws.da_addr(pt.stage), pt.nt * 64);
+      const int nbox = (p_nt + 3) >> 2;
+#pragma unroll
+      for (int b = 0; b < NBOX; ++b)
+        if (b < nbox) tma_store_2d(&tm_dx, p_c0 + 64 * b, p_bh * 16, ws.x(p_stage) + b * 2048);
+      bulk_store(p.dA + static_cast<long long>(p_bh) * L + p_c0, ws.tab_addr(p_stage) + 3 * TL * 4, p_nt * 64);
       bulk_commit_group();
-      if (issued < n) {
-        // the next load goes into the stage of the chunk flushed one chunk earlier
-        bulk_wait_group_read<1>();
-        issue(issued);
-      }
+      if (issued < n) bulk_wait_group_read<1>();  // the store flushed one chunk earlier has drained
     }
-    if (issued < n) ++issued;
+    if (issued < n) issue();
   };
 
-  TileAcc cur, nxt;
-  PendingTile pend;
-  bool have = false;
-  bool failed = false;
-  int fail_chunk = 0;
-  float vl_g = 0.0f, vl_g8 = 0.0f;  // uncorrected last token of the most recent block
-
-  for (int j = 0; j < n && !failed; ++j) {
-    const int s = j % STAGES;
-    const ChunkPos c = chunk_pos<TL>(cb + j, p.ncs, p.L);
-    if (!mbar_wait_bounded(ws.bar(s), (j / STAGES) & 1, kWaitLimitNs)) {
+  int j = 0, s = 0;
+  uint32_t phase = 0;
+  for (; j < n; ++j) {
+    if (!mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs)) {
       failed = true;
-      fail_chunk = j;
       break;
     }
-    coeff_to_prefix<COEF, TL>(ws.t_ptr(s), lane);
-    if (j == 0 && c.cs != 0 && p.use_carry) {
-      halo_reduce<COEF, false, false>(p.x, p.coeff, p.L, c.bh, c.c0 - 16, lane, vl_g, vl_g8);
+    const int nt = chunk_tiles<TL>(cons.cs, L);
+    const int c0 = cons.cs * TL;
+    float* tab = ws.tab_ptr(s);
+    chunk_tables<COEF, TL, true>(tab, lane);
+    if (j == 0 && cons.cs != 0 && p.use_carry) {
+      halo_reduce<COEF, false, false>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
     }
-    for (int i = 0; i < c.nt; ++i) {
-      float dc_g, dc_g8;
-      __syncwarp();
-      front(s, i, nxt, dc_g, dc_g8);
-      if (have) {
-        const bool cut = pend.seq_end || !p.use_carry;
-        back(pend, cur, cut ? 0.0f : dc_g, cut ? 0.0f : dc_g8);
-        if (pend.chunk_end) flush(pend);
+    const float* tg = tab + tl.g;
+    const float* tt = tab + 2 * tl.t;
+    float* da = tab + 3 * TL;
+    const uint32_t xs = ws.x(s);
+    const uint32_t ldm = xs + tl.ldm_base;
+    const uint32_t stb = xs + tl.st_base;
+    const bool seq_first = (cons.cs == 0);
+    const bool carry_on = p.use_carry != 0;
+
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      if (i < nt) {
+        TileAcc& cur = (i & 1) ? accB : accA;         // block i
+        const TileAcc& prev = (i & 1) ? accA : accB;  // block i-1 (slot B holds the pending one when i == 0)
+        float dc_g, dc_g8;
+        front(tab, tg, tt, ldm, ws.dy(s), i, cur, dc_g, dc_g8);
+        if (!carry_on) dc_g = dc_g8 = 0.0f;
+        const float ncg = ((i == 0 && seq_first) || !carry_on) ? 0.0f : vl_g;  // carry into block i
+        const float ncg8 = ((i == 0 && seq_first) || !carry_on) ? 0.0f : vl_g8;
+        if (i == 0) {
+          if (have) {
+            back(prev, p_tt, p_da, p_o0, p_cg, p_cg8, p_seq_end ? 0.0f : dc_g, p_seq_end ? 0.0f : dc_g8);
+            flush();
+          }
+        } else {
+          const int pi = i - 1;
+          back(prev, tt + 16 * pi, da + 16 * pi, stb + (pi >> 2) * 2048 + tl.st_off[pi & 3], p_cg, p_cg8, dc_g, dc_g8);
+        }
+        p_cg = ncg;
+        p_cg8 = ncg8;
+        vl_g = __shfl_sync(0xffffffffu, cur.v1[1], lane | 3);
+        vl_g8 = __shfl_sync(0xffffffffu, cur.v1[3], lane | 3);
       }
-      const bool seq_start = (c.cs == 0 && i == 0);
-      pend.stage = s;
-      pend.i = i;
-      pend.cg = (seq_start || !p.use_carry) ? 0.0f : vl_g;
-      pend.cg8 = (seq_start || !p.use_carry) ? 0.0f : vl_g8;
-      pend.seq_end = (c.cs == p.ncs - 1) && (i == c.nt - 1);
-      pend.chunk_end = (i == c.nt - 1);
-      pend.bh = c.bh;
-      pend.c0 = c.c0;
-      pend.nt = c.nt;
-      cur = nxt;
-      have = true;
-      const int src = lane | 3;
-      vl_g = __shfl_sync(0xffffffffu, cur.v1[1], src);
-      vl_g8 = __shfl_sync(0xffffffffu, cur.v1[3], src);
+    }
+    // the chunk's last block becomes the pending one (slot B)
+    if ((nt & 1) != 0) accB = accA;
+    have = true;
+    p_seq_end = (cons.cs == ncs - 1);
+    p_tt = tt + 16 * (nt - 1);
+    p_da = da + 16 * (nt - 1);
+    p_o0 = stb + ((nt - 1) >> 2) * 2048 + (((2u * ((nt - 1) & 3)) ^ static_cast<uint32_t>(tl.g)) << 4);
+    p_stage = s;
+    p_bh = cons.bh;
+    p_c0 = c0;
+    p_nt = nt;
+    cons.next(ncs);
+    if (++s == STAGES) {
+      s = 0;
+      phase ^= 1u;
     }
   }
 
   if (!failed && have) {
     float dc_g = 0.0f, dc_g8 = 0.0f;
-    if (!pend.seq_end && p.use_carry) {
+    if (!p_seq_end && p.use_carry) {
       // the block to the right belongs to another warp: recompute what it sends
-      halo_reduce<COEF, DY_F32, true>(p.dy, p.coeff, p.L, pend.bh, pend.c0 + 16 * pend.nt, lane, dc_g, dc_g8);
+      halo_reduce<COEF, DY_F32, true>(p.dy, p.coeff, L, p_bh, p_c0 + 16 * p_nt, lane, dc_g, dc_g8);
     }
-    back(pend, cur, dc_g, dc_g8);
-    flush(pend);
+    back(accB, p_tt, p_da, p_o0, p_cg, p_cg8, dc_g, dc_g8);
+    flush();
   }
   if (failed) {
-    if (lane == 0) report_timeout(warp, cb + fail_chunk);
-    for (int j = fail_chunk; j < issued; ++j) mbar_wait_bounded(ws.bar(j % STAGES), (j / STAGES) & 1, kWaitLimitNs);
+    if (lane == 0) report_timeout(warp, cb + j);
+    for (int k = j; k < issued; ++k) {
+      mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs);
+      if (++s == STAGES) {
+        s = 0;
+        phase ^= 1u;
+      }
+    }
   }
   if (lane == 0) bulk_wait_group<0>();
 }

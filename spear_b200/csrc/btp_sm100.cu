@@ -203,8 +203,9 @@ int forward_variant(const void* coeff, const void* x, void* y, float* ckpt, Dims
     switch (variant()) {
       case 1: return launch_forward<COEF, OUT_F32, CKPT, 2, 4, 4>(coeff, x, y, ckpt, d, k, s);
       case 2: return launch_forward<COEF, OUT_F32, CKPT, 1, 4, 4>(coeff, x, y, ckpt, d, k, s);
-      case 3: return launch_forward<COEF, OUT_F32, CKPT, 1, 6, 4>(coeff, x, y, ckpt, d, k, s);
+      case 3: return launch_forward<COEF, OUT_F32, CKPT, 1, 3, 4>(coeff, x, y, ckpt, d, k, s);
       case 4: return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 8>(coeff, x, y, ckpt, d, k, s);
+      case 5: return launch_forward<COEF, OUT_F32, CKPT, 1, 6, 4>(coeff, x, y, ckpt, d, k, s);
       default: break;
     }
   }
@@ -253,14 +254,15 @@ template <int COEF, bool DY_F32>
 int backward_variant(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k, cudaStream_t s) {
   if constexpr (COEF == kCoefBf16 && !DY_F32) {
     switch (variant()) {
-      case 1: return launch_backward<COEF, DY_F32, 2, 4, 2>(coeff, x, dy, dx, dA, d, k, s);
+      case 1: return launch_backward<COEF, DY_F32, 2, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
       case 2: return launch_backward<COEF, DY_F32, 1, 4, 4>(coeff, x, dy, dx, dA, d, k, s);
-      case 3: return launch_backward<COEF, DY_F32, 1, 6, 4>(coeff, x, dy, dx, dA, d, k, s);
-      case 4: return launch_backward<COEF, DY_F32, 2, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
+      case 3: return launch_backward<COEF, DY_F32, 1, 3, 8>(coeff, x, dy, dx, dA, d, k, s);
+      case 4: return launch_backward<COEF, DY_F32, 1, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
+      case 5: return launch_backward<COEF, DY_F32, 1, 3, 7>(coeff, x, dy, dx, dA, d, k, s);
       default: break;
     }
   }
-  return launch_backward<COEF, DY_F32, 2, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
+  return launch_backward<COEF, DY_F32, 1, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
 }
 
 }  // namespace
