@@ -55,6 +55,7 @@ struct KernelParams {
   int ncs;             // chunks per sequence
   int total_chunks;    // BH * ncs
   int use_carry;       // k == 2
+  int interleave;      // deal whole sequences round-robin to the warps (short sequences)
 };
 
 template <int COEF>
@@ -72,61 +73,97 @@ __device__ __forceinline__ float coef_log2(float a) {
   }
 }
 
-// Shared-memory carve-up of one CTA.  Every warp owns STAGES stages; a stage holds the tiles of one
-// chunk ("big": x, and dy for backward) and its per-token float tables ("small", kTables x TL floats):
-//   forward : T, P                 backward: T, Pshift (P[t-1], 1 at t=0), L15 (last Lmat row), dA staging
-template <int NBOX, int STAGES, int WARPS, bool BWD, bool DY_F32>
+// Shared-memory carve-up of one CTA.  Every warp owns
+//   * STAGES buffers for the x tiles of a chunk (NBOX boxes of [16][64] bf16, 128-byte swizzled); a bf16
+//     output (y, dx) is written over them and leaves from there,
+//   * backward: STAGES-1 buffers for the dy tiles (they are dead as soon as the chunk's products are done),
+//   * STAGES landing zones for the raw coefficients, backward: STAGES staging rows for dA,
+//   * the per-token float tables of the chunk in work (forward: T, P; backward, double-buffered because a
+//     chunk's last block is finished one block into the next chunk: T, Pshift, L15),
+//   * STAGES mbarriers.
+template <int COEF, int NBOX, int STAGES, int WARPS, bool BWD, bool DY_F32>
 struct SmemLayout {
   static constexpr int kTL = 64 * NBOX;                 // tokens per chunk
   static constexpr int kTiles = kTL / 16;               // 16-token blocks per chunk
-  static constexpr int kXBytes = NBOX * 2048;           // [16][64] bf16 per box
+  static constexpr int kXBytes = NBOX * 2048;
   static constexpr int kDyBytes = BWD ? (DY_F32 ? NBOX * 4096 : NBOX * 2048) : 0;
-  static constexpr int kBigPerStage = kXBytes + kDyBytes;  // multiple of 1024 (swizzle atom)
-  static constexpr int kTables = BWD ? 4 : 2;
-  static constexpr int kSmallPerStage = kTables * kTL * 4;
-  static constexpr int kBigTotal = WARPS * STAGES * kBigPerStage;
-  static constexpr int kSmallTotal = WARPS * STAGES * kSmallPerStage;
-  static constexpr int kBarTotal = WARPS * STAGES * 8;
-  static constexpr int kBytes = kBigTotal + kSmallTotal + kBarTotal + 1024;  // + slack to align the base
+  static constexpr int kDyStages = BWD ? STAGES - 1 : 0;
+  static constexpr int kBigPerWarp = STAGES * kXBytes + kDyStages * kDyBytes;  // multiple of 1024 (swizzle atom)
+  static constexpr int kRawBytes = kTL * CoefTraits<COEF>::kBytes;
+  static constexpr int kDaBytes = BWD ? kTL * 4 : 0;
+  static constexpr int kTabFloats = (BWD ? 3 : 2) * kTL;
+  static constexpr int kTabSets = BWD ? 2 : 1;
+  static constexpr int kSmallPerWarp = STAGES * (kRawBytes + kDaBytes) + kTabSets * kTabFloats * 4;
+  static constexpr int kBarsPerWarp = STAGES * 8;
+  static constexpr int kBytes = WARPS * (kBigPerWarp + kSmallPerWarp + kBarsPerWarp);
 };
 
-// Per-warp view of its stages.
-template <class LAYOUT>
+// Per-warp view of its buffers (shared-space addresses for the async copies, generic pointers for the tables).
+template <class LAYOUT, int STAGES>
 struct WarpSmem {
-  uint32_t big;    // shared-space address of stage 0 of the tile buffers
-  uint32_t small;  // ... of the tables
-  uint32_t bars;   // ... of the mbarriers
-  unsigned char* small_ptr;  // generic pointer to `small`
-  __device__ __forceinline__ uint32_t x(int s) const { return big + s * LAYOUT::kBigPerStage; }
-  __device__ __forceinline__ uint32_t dy(int s) const { return x(s) + LAYOUT::kXBytes; }
-  __device__ __forceinline__ uint32_t tab_addr(int s) const { return small + s * LAYOUT::kSmallPerStage; }
-  __device__ __forceinline__ float* tab_ptr(int s) const {
-    return reinterpret_cast<float*>(small_ptr + s * LAYOUT::kSmallPerStage);
+  uint32_t big, small, bars;
+  unsigned char* small_ptr;
+  __device__ __forceinline__ uint32_t x(int s) const { return big + s * LAYOUT::kXBytes; }
+  __device__ __forceinline__ uint32_t dy(int d) const { return big + STAGES * LAYOUT::kXBytes + d * LAYOUT::kDyBytes; }
+  __device__ __forceinline__ uint32_t raw_addr(int s) const { return small + s * LAYOUT::kRawBytes; }
+  __device__ __forceinline__ const void* raw_ptr(int s) const { return small_ptr + s * LAYOUT::kRawBytes; }
+  __device__ __forceinline__ uint32_t da_addr(int s) const { return small + STAGES * LAYOUT::kRawBytes + s * LAYOUT::kDaBytes; }
+  __device__ __forceinline__ float* da_ptr(int s) const {
+    return reinterpret_cast<float*>(small_ptr + STAGES * LAYOUT::kRawBytes + s * LAYOUT::kDaBytes);
+  }
+  __device__ __forceinline__ float* tab_ptr(int set) const {
+    return reinterpret_cast<float*>(small_ptr + STAGES * (LAYOUT::kRawBytes + LAYOUT::kDaBytes) + set * LAYOUT::kTabFloats * 4);
   }
   __device__ __forceinline__ uint32_t bar(int s) const { return bars + s * 8; }
 };
 
-template <class LAYOUT, int STAGES>
-__device__ __forceinline__ WarpSmem<LAYOUT> carve_smem(unsigned char* raw, int warp) {
+template <class LAYOUT, int STAGES, int WARPS>
+__device__ __forceinline__ WarpSmem<LAYOUT, STAGES> carve_smem(unsigned char* raw, int warp) {
   const uint32_t base = smem_u32(raw);
-  const uint32_t pad = (1024u - (base & 1023u)) & 1023u;
-  WarpSmem<LAYOUT> w;
-  w.big = base + pad + warp * STAGES * LAYOUT::kBigPerStage;
-  w.small = base + pad + LAYOUT::kBigTotal + warp * STAGES * LAYOUT::kSmallPerStage;
-  w.small_ptr = raw + pad + LAYOUT::kBigTotal + warp * STAGES * LAYOUT::kSmallPerStage;
-  w.bars = base + pad + LAYOUT::kBigTotal + LAYOUT::kSmallTotal + warp * STAGES * 8;
+  WarpSmem<LAYOUT, STAGES> w;
+  w.big = base + warp * LAYOUT::kBigPerWarp;
+  w.small = base + WARPS * LAYOUT::kBigPerWarp + warp * LAYOUT::kSmallPerWarp;
+  w.small_ptr = raw + WARPS * LAYOUT::kBigPerWarp + warp * LAYOUT::kSmallPerWarp;
+  w.bars = base + WARPS * (LAYOUT::kBigPerWarp + LAYOUT::kSmallPerWarp) + warp * LAYOUT::kBarsPerWarp;
   return w;
 }
 
 // Position of a chunk; walks forward one chunk at a time (no division after the first).
 struct ChunkCursor {
-  int bh;  // sequence index
-  int cs;  // chunk index inside the sequence
-  __device__ __forceinline__ ChunkCursor(int id, int ncs) : bh(id / ncs), cs(id - (id / ncs) * ncs) {}
+  int bh;    // sequence index
+  int cs;    // chunk index inside the sequence
+  int step;  // distance, in sequences, from one sequence of this warp to its next
+  __device__ __forceinline__ ChunkCursor(int bh_, int cs_, int step_) : bh(bh_), cs(cs_), step(step_) {}
   __device__ __forceinline__ void next(int ncs) {
     if (++cs == ncs) {
       cs = 0;
-      ++bh;
+      bh += step;
+    }
+  }
+};
+
+// Which chunks a warp works on.
+//   Long sequences (or too few of them to balance): a contiguous range of the (sequence, chunk) list, so
+//   that the carry runs along the sequence in registers and only the two ends of the range need a halo.
+//   Short sequences: whole sequences dealt round-robin to the warps, so that at any moment the whole GPU
+//   reads and writes one moving window of memory (measurably kinder to HBM than 2368 separate streams).
+struct WarpWork {
+  int bh, cs;  // first chunk
+  int n;       // number of chunks
+  int step;    // sequences between consecutive sequences of this warp
+  __device__ __forceinline__ WarpWork(long long wid, long long nwarps, int total, int ncs, bool interleave) {
+    if (interleave) {
+      const long long nseq = total / ncs;
+      bh = static_cast<int>(wid);
+      cs = 0;
+      step = static_cast<int>(nwarps);
+      n = wid < nseq ? static_cast<int>((nseq - wid + nwarps - 1) / nwarps) * ncs : 0;
+    } else {
+      const int first = static_cast<int>((wid * total) / nwarps);
+      n = static_cast<int>(((wid + 1) * total) / nwarps) - first;
+      bh = first / ncs;
+      cs = first - bh * ncs;
+      step = 1;
     }
   }
 };
@@ -137,29 +174,29 @@ __device__ __forceinline__ int chunk_tiles(int cs, int L) {
   return left < TL / 16 ? left : TL / 16;
 }
 
-// Once per chunk: raw coefficients (already in shared memory at tab[0..]) -> per-token tables.
+// Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables at `tab`.
 // Lane l owns TPL = TL/32 consecutive tokens; 16/TPL lanes make one block; the prefix sums restart
 // at every block.  Tables (each TL floats): [0] T, then forward [1] P = 2^T,
 // backward [1] Pshift (P of the previous token, 1 for the first token of a block), [2] L15 = 2^(T_15 - T).
 template <int COEF, int TL, bool BWD>
-__device__ __forceinline__ void chunk_tables(float* tab, int lane) {
+__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane) {
   constexpr int TPL = TL / 32;    // tokens per lane: 2 or 4
   constexpr int LPT = 16 / TPL;   // lanes per block: 8 or 4
   float v[TPL];
   if constexpr (COEF == kCoefBf16) {
     if constexpr (TPL == 4) {
-      const uint2 raw = reinterpret_cast<const uint2*>(tab)[lane];
+      const uint2 raw = reinterpret_cast<const uint2*>(rawp)[lane];
       v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
     } else {
-      const uint32_t raw = reinterpret_cast<const uint32_t*>(tab)[lane];
+      const uint32_t raw = reinterpret_cast<const uint32_t*>(rawp)[lane];
       v[0] = bf16_lo(raw); v[1] = bf16_hi(raw);
     }
   } else {
     if constexpr (TPL == 4) {
-      const float4 raw = reinterpret_cast<const float4*>(tab)[lane];
+      const float4 raw = reinterpret_cast<const float4*>(rawp)[lane];
       v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
     } else {
-      const float2 raw = reinterpret_cast<const float2*>(tab)[lane];
+      const float2 raw = reinterpret_cast<const float2*>(rawp)[lane];
       v[0] = raw.x; v[1] = raw.y;
     }
   }
@@ -200,7 +237,7 @@ __device__ __forceinline__ void chunk_tables(float* tab, int lane) {
       third[k] = 0.0f;
     }
   }
-  __syncwarp();  // every lane has read its raw coefficients
+  __syncwarp();  // nobody still reads the tables of the chunk before
   if constexpr (TPL == 4) {
     reinterpret_cast<float4*>(tab)[lane] = make_float4(T[0], T[1], T[2], T[3]);
     reinterpret_cast<float4*>(tab + TL)[lane] = make_float4(second[0], second[1], second[2], second[3]);
@@ -336,8 +373,9 @@ __device__ __forceinline__ LmatFrag build_lmat(const float* tg, const float* tt,
   return f;
 }
 
-__device__ __forceinline__ void report_timeout(int warp, int chunk) {
-  if (atomicCAS(&g_btp_device_error[0], 0u, 1u) == 0u) {
+// code 1: a bounded wait gave up; code 2: shared-memory base not 1024-byte aligned
+__device__ __forceinline__ void report_error(unsigned int code, int warp, int chunk) {
+  if (atomicCAS(&g_btp_device_error[0], 0u, code) == 0u) {
     g_btp_device_error[1] = blockIdx.x;
     g_btp_device_error[2] = warp;
     g_btp_device_error[3] = chunk;
@@ -351,7 +389,7 @@ template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const KernelParams p) {
-  using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, false, false>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
   constexpr int TL = LAYOUT::kTL;
   constexpr int NT = LAYOUT::kTiles;
   constexpr int kEsz = CoefTraits<COEF>::kBytes;
@@ -360,19 +398,22 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   constexpr int AHEAD = OUT_F32 ? STAGES - 1 : STAGES - 2;
   static_assert(AHEAD >= 1, "need more stages");
 
-  extern __shared__ unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const WarpSmem<LAYOUT> ws = carve_smem<LAYOUT, STAGES>(smem_raw, warp);
+  const WarpSmem<LAYOUT, STAGES> ws = carve_smem<LAYOUT, STAGES, WARPS>(smem_raw, warp);
   const TileLane tl(lane);
 
   // contiguous range of chunks for this warp
   const long long nwarps = static_cast<long long>(gridDim.x) * WARPS;
   const long long wid = static_cast<long long>(blockIdx.x) * WARPS + warp;
-  const int cb = static_cast<int>((wid * p.total_chunks) / nwarps);
-  const int ce = static_cast<int>(((wid + 1) * p.total_chunks) / nwarps);
-  const int n = ce - cb;
+  const WarpWork work(wid, nwarps, p.total_chunks, p.ncs, p.interleave != 0);
+  const int n = work.n;
   if (n <= 0) return;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled boxes need a 1024-byte aligned base
+    if (lane == 0) report_error(2u, warp, 0);
+    return;
+  }
 
   if (lane == 0) {
 #pragma unroll
@@ -385,7 +426,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   __syncwarp();
 
   const int L = p.L, ncs = p.ncs;
-  ChunkCursor prod(cb, ncs), cons(cb, ncs);
+  ChunkCursor prod(work.bh, work.cs, work.step), cons(work.bh, work.cs, work.step);
   int s_prod = 0;
   auto issue = [&]() {  // starts the loads of the producer cursor's chunk into stage s_prod, then advances
     if (lane == 0) {
@@ -398,7 +439,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
       for (int b = 0; b < NBOX; ++b)
         if (b < nbox) tma_load_2d(ws.x(s_prod) + b * 2048, &tm_x, c0 + 64 * b, prod.bh * 16, bar);
-      bulk_load(ws.tab_addr(s_prod),
+      bulk_load(ws.raw_addr(s_prod),
                 reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(prod.bh) * L + c0) * kEsz, cbytes, bar);
     }
     prod.next(ncs);
@@ -423,8 +464,8 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
     const int nt = chunk_tiles<TL>(cons.cs, L);
     const int c0 = cons.cs * TL;
-    float* tab = ws.tab_ptr(s);
-    chunk_tables<COEF, TL, false>(tab, lane);
+    float* tab = ws.tab_ptr(0);
+    chunk_tables<COEF, TL, false>(ws.raw_ptr(s), tab, lane);
 
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
@@ -502,8 +543,6 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           if (b < nbox) tma_store_2d(&tm_y, c0 + 64 * b, cons.bh * 16, xs + b * 2048);
         bulk_commit_group();
       }
-    } else {
-      __syncwarp();  // the tables of this stage are free again
     }
     cons.next(ncs);
     if (++s == STAGES) {
@@ -513,7 +552,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   }
 
   if (failed) {
-    if (lane == 0) report_timeout(warp, cb + j);
+    if (lane == 0) report_error(1u, warp, cons.bh * ncs + cons.cs);
     // give the loads still in flight a (bounded) chance to land before the buffers are released
     for (int k = j; k < n && k <= j + AHEAD; ++k) {
       mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs);
@@ -538,24 +577,27 @@ template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                     const __grid_constant__ CUtensorMap tm_dx, const KernelParams p) {
-  using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, true, DY_F32>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, true, DY_F32>;
   constexpr int TL = LAYOUT::kTL;
   constexpr int NT = LAYOUT::kTiles;
   constexpr int kEsz = CoefTraits<COEF>::kBytes;
   static_assert(STAGES >= 3, "the backward ring needs three stages");
 
-  extern __shared__ unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const WarpSmem<LAYOUT> ws = carve_smem<LAYOUT, STAGES>(smem_raw, warp);
+  const WarpSmem<LAYOUT, STAGES> ws = carve_smem<LAYOUT, STAGES, WARPS>(smem_raw, warp);
   const TileLane tl(lane);
 
   const long long nwarps = static_cast<long long>(gridDim.x) * WARPS;
   const long long wid = static_cast<long long>(blockIdx.x) * WARPS + warp;
-  const int cb = static_cast<int>((wid * p.total_chunks) / nwarps);
-  const int ce = static_cast<int>(((wid + 1) * p.total_chunks) / nwarps);
-  const int n = ce - cb;
+  const WarpWork work(wid, nwarps, p.total_chunks, p.ncs, p.interleave != 0);
+  const int n = work.n;
   if (n <= 0) return;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled boxes need a 1024-byte aligned base
+    if (lane == 0) report_error(2u, warp, 0);
+    return;
+  }
 
   if (lane == 0) {
 #pragma unroll
@@ -569,8 +611,8 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   __syncwarp();
 
   const int L = p.L, ncs = p.ncs;
-  ChunkCursor prod(cb, ncs), cons(cb, ncs);
-  int s_prod = 0, issued = 0;
+  ChunkCursor prod(work.bh, work.cs, work.step), cons(work.bh, work.cs, work.step);
+  int s_prod = 0, d_prod = 0, issued = 0;
   auto issue = [&]() {
     if (lane == 0) {
       const int nt = chunk_tiles<TL>(prod.cs, L);
@@ -585,23 +627,25 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (b < nbox) tma_load_2d(ws.x(s_prod) + b * 2048, &tm_x, c0 + 64 * b, prod.bh * 16, bar);
 #pragma unroll
       for (int b = 0; b < (DY_F32 ? 2 * NBOX : NBOX); ++b)
-        if (b < nbox_dy) tma_load_2d(ws.dy(s_prod) + b * 2048, &tm_dy, c0 + (DY_F32 ? 32 : 64) * b, prod.bh * 16, bar);
-      bulk_load(ws.tab_addr(s_prod),
+        if (b < nbox_dy) tma_load_2d(ws.dy(d_prod) + b * 2048, &tm_dy, c0 + (DY_F32 ? 32 : 64) * b, prod.bh * 16, bar);
+      bulk_load(ws.raw_addr(s_prod),
                 reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(prod.bh) * L + c0) * kEsz, cbytes, bar);
     }
     prod.next(ncs);
     s_prod = (s_prod + 1 == STAGES) ? 0 : s_prod + 1;
+    d_prod = (d_prod + 1 == STAGES - 1) ? 0 : d_prod + 1;
     ++issued;
   };
 
   // Chunk j's outputs leave one block into chunk j+1 (its last block needs the gradient that
-  // arrives from the right).  The stage of chunk j is reloaded one chunk later still, when that
-  // store has certainly drained: loads run STAGES-2 chunks ahead.
+  // arrives from the right).  The x buffer of chunk j is reloaded one chunk later still, when that
+  // store has certainly drained; the dy buffer of chunk j is free once chunk j's products are done.
+  // Loads therefore run STAGES-2 chunks ahead, and STAGES-1 dy buffers are enough.
   while (issued < STAGES - 1 && issued < n) issue();
 
   // ---- front half of a block: Lmat fragments and the four tensor-core products
   auto front = [&](const float* tab, const float* tg, const float* tt, uint32_t ldm_x, uint32_t dy_s, int i,
-                   TileAcc& acc, float& dc_g, float& dc_g8) {
+                   TileAcc& acc, float& dc_g, float& dc_g8) {  // dy_s: the chunk's dy buffer
     const int box = i >> 2, ib = i & 3;
     const LmatFrag lf = build_lmat(tg, tt, 16 * i, tl);
     // dy . Lmat needs the transposed 8x8 blocks as B operand (k = r, n = c)
@@ -626,7 +670,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       f = lds(bb + ((c_hi ^ tl.g) << 4) + in);         e2 = pack_bf16x2(f.x, f.y);
       f = lds(bb + 1024 + ((c_hi ^ tl.g) << 4) + in);  e3 = pack_bf16x2(f.x, f.y);
     } else {
-      ldmatrix_x4(ldm_x + LAYOUT::kXBytes + box * 2048 + tl.ldm_off[ib], e0, e1, e2, e3);
+      ldmatrix_x4(dy_s + tl.ldm_base + box * 2048 + tl.ldm_off[ib], e0, e1, e2, e3);
     }
     mma_1688(acc.v0, a0, a1, lf.b00);
     mma_16816(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
@@ -715,14 +759,14 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 #pragma unroll
       for (int b = 0; b < NBOX; ++b)
         if (b < nbox) tma_store_2d(&tm_dx, p_c0 + 64 * b, p_bh * 16, ws.x(p_stage) + b * 2048);
-      bulk_store(p.dA + static_cast<long long>(p_bh) * L + p_c0, ws.tab_addr(p_stage) + 3 * TL * 4, p_nt * 64);
+      bulk_store(p.dA + static_cast<long long>(p_bh) * L + p_c0, ws.da_addr(p_stage), p_nt * 64);
       bulk_commit_group();
       if (issued < n) bulk_wait_group_read<1>();  // the store flushed one chunk earlier has drained
     }
     if (issued < n) issue();
   };
 
-  int j = 0, s = 0;
+  int j = 0, s = 0, d = 0, tset = 0;
   uint32_t phase = 0;
   for (; j < n; ++j) {
     if (!mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs)) {
@@ -731,15 +775,16 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     }
     const int nt = chunk_tiles<TL>(cons.cs, L);
     const int c0 = cons.cs * TL;
-    float* tab = ws.tab_ptr(s);
-    chunk_tables<COEF, TL, true>(tab, lane);
+    float* tab = ws.tab_ptr(tset);
+    chunk_tables<COEF, TL, true>(ws.raw_ptr(s), tab, lane);
     if (j == 0 && cons.cs != 0 && p.use_carry) {
       halo_reduce<COEF, false, false>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
     }
     const float* tg = tab + tl.g;
     const float* tt = tab + 2 * tl.t;
-    float* da = tab + 3 * TL;
+    float* da = ws.da_ptr(s);
     const uint32_t xs = ws.x(s);
+    const uint32_t dys = ws.dy(d);
     const uint32_t ldm = xs + tl.ldm_base;
     const uint32_t stb = xs + tl.st_base;
     const bool seq_first = (cons.cs == 0);
@@ -751,7 +796,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         TileAcc& cur = (i & 1) ? accB : accA;         // block i
         const TileAcc& prev = (i & 1) ? accA : accB;  // block i-1 (slot B holds the pending one when i == 0)
         float dc_g, dc_g8;
-        front(tab, tg, tt, ldm, ws.dy(s), i, cur, dc_g, dc_g8);
+        front(tab, tg, tt, ldm, dys, i, cur, dc_g, dc_g8);
         if (!carry_on) dc_g = dc_g8 = 0.0f;
         const float ncg = ((i == 0 && seq_first) || !carry_on) ? 0.0f : vl_g;  // carry into block i
         const float ncg8 = ((i == 0 && seq_first) || !carry_on) ? 0.0f : vl_g8;
@@ -782,6 +827,8 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     p_c0 = c0;
     p_nt = nt;
     cons.next(ncs);
+    tset ^= 1;
+    if (++d == STAGES - 1) d = 0;
     if (++s == STAGES) {
       s = 0;
       phase ^= 1u;
@@ -798,7 +845,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     flush();
   }
   if (failed) {
-    if (lane == 0) report_timeout(warp, cb + j);
+    if (lane == 0) report_error(1u, warp, cons.bh * ncs + cons.cs);
     for (int k = j; k < issued; ++k) {
       mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs);
       if (++s == STAGES) {

@@ -165,12 +165,22 @@ int set_chunks(const char* fn, Dims* d, int TL) {
   return BTP_OK;
 }
 
+// Whole sequences are dealt round-robin to the warps when they are short (at most 8 chunks) and numerous
+// enough (at least 4 per warp) for that to balance; otherwise every warp takes a contiguous range of chunks.
+bool use_interleave(const Dims& d, long long nwarps) {
+  static const bool enabled = [] {
+    const char* e = getenv("BTP_SM100_INTERLEAVE");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return enabled && d.ncs <= 8 && d.BH >= 4 * nwarps;
+}
+
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 // ------------------------------------------------------------------ forward dispatch
 template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
 int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
-  using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, false, false>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
   auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, NBOX, STAGES, WARPS>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
@@ -187,10 +197,11 @@ int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims 
   } else if ((rc = make_map(&tm_y, y, false, d.BH * 16, d.L))) {
     return rc;
   }
+  const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
   KernelParams p{};
   p.coeff = coeff; p.x = x; p.out_f32 = y; p.ckpt = ckpt;
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
-  const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
+  p.interleave = use_interleave(d, static_cast<long long>(grid) * WARPS);
   kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_y, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -226,7 +237,7 @@ int forward_coef(const void* coeff, const void* x, void* y, float* ckpt, Dims d,
 template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
 int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
                     cudaStream_t stream) {
-  using LAYOUT = SmemLayout<NBOX, STAGES, WARPS, true, DY_F32>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, true, DY_F32>;
   auto kern = btp_backward_kernel<COEF, DY_F32, NBOX, STAGES, WARPS>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
@@ -240,10 +251,11 @@ int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, 
   if ((rc = make_map(&tm_x, x, false, d.BH * 16, d.L))) return rc;
   if ((rc = make_map(&tm_dy, dy, DY_F32, d.BH * 16, d.L))) return rc;
   if ((rc = make_map(&tm_dx, dx, false, d.BH * 16, d.L))) return rc;
+  const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
   KernelParams p{};
   p.coeff = coeff; p.x = x; p.dy = dy; p.dA = dA;
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
-  const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
+  p.interleave = use_interleave(d, static_cast<long long>(grid) * WARPS);
   kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_dy, tm_dx, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -254,11 +266,11 @@ template <int COEF, bool DY_F32>
 int backward_variant(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k, cudaStream_t s) {
   if constexpr (COEF == kCoefBf16 && !DY_F32) {
     switch (variant()) {
-      case 1: return launch_backward<COEF, DY_F32, 2, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
-      case 2: return launch_backward<COEF, DY_F32, 1, 4, 4>(coeff, x, dy, dx, dA, d, k, s);
-      case 3: return launch_backward<COEF, DY_F32, 1, 3, 8>(coeff, x, dy, dx, dA, d, k, s);
-      case 4: return launch_backward<COEF, DY_F32, 1, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
-      case 5: return launch_backward<COEF, DY_F32, 1, 3, 7>(coeff, x, dy, dx, dA, d, k, s);
+      case 1: return launch_backward<COEF, DY_F32, 1, 4, 4>(coeff, x, dy, dx, dA, d, k, s);
+      case 2: return launch_backward<COEF, DY_F32, 1, 3, 8>(coeff, x, dy, dx, dA, d, k, s);
+      case 3: return launch_backward<COEF, DY_F32, 1, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
+      case 4: return launch_backward<COEF, DY_F32, 2, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
+      case 5: return launch_backward<COEF, DY_F32, 1, 4, 3>(coeff, x, dy, dx, dA, d, k, s);
       default: break;
     }
   }
@@ -340,7 +352,9 @@ int btp_sm100_device_status(void* stream, unsigned int* detail) {
   if (words[0] == 0) return BTP_OK;
   const unsigned int zero[4] = {0, 0, 0, 0};
   BTP_CUDA_TRY(cudaMemcpyToSymbol(btp::g_btp_device_error, zero, sizeof(zero)));
-  return fail(BTP_ERR_DEVICE_TIMEOUT, "a kernel wait gave up: block %u warp %u chunk %u", words[1], words[2], words[3]);
+  return fail(BTP_ERR_DEVICE_TIMEOUT, "%s: block %u warp %u chunk %u",
+              words[0] == 2 ? "shared-memory base not 1024-byte aligned" : "a kernel wait gave up", words[1], words[2],
+              words[3]);
 }
 
 unsigned long long btp_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
