@@ -291,12 +291,10 @@ def main():
 
     # ---- max over ranks
     if dist is not None:
-        t = torch.tensor([total_ms, e2e_ms, fwd_us, bwd_us], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, fwd_us, bwd_us = t.tolist()
-        lt = torch.tensor([launches], device=dev, dtype=torch.int64)
-        dist.all_reduce(lt)
-        launches = int(lt.item())
+        from spear_b200.sharding import max_over_ranks, sum_over_ranks
+
+        total_ms, e2e_ms, fwd_us, bwd_us = max_over_ranks([total_ms, e2e_ms, fwd_us, bwd_us], device=dev)
+        launches = int(sum_over_ranks([launches], device=dev)[0])
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -313,7 +311,7 @@ def main():
             "config": {
                 "workload": f"btp fwd+bwd B={B} H={H} L={L} head_dim={D} block=16 per GPU (configs[2]); "
                             "x~N(0,1/16) bf16, coeff=exp(-softplus(N(0,1))) bf16, dy~N(0,1) bf16",
-                "l2": f"each step touches 705 MB (> 126 MB L2) and {NSETS} input/output sets rotate",
+                "l2": f"each step touches {168 * B * H * L / 1e6:.0f} MB (L2 holds 126 MB) and {NSETS} input/output sets rotate",
                 "parallelism": f"batch sharded over {world} GPU(s), no data-path collective",
             },
             "e2e": {"value": world * B * L * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,

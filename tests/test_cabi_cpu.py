@@ -1,0 +1,116 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every symbol that
+include/btp_sm100.h declares, names its status codes, and rejects bad arguments before
+touching CUDA.  No compute call is made."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+HEADER = os.path.join(ROOT, "include", "btp_sm100.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from spear_b200 import _lib, build
+
+    build.build()  # no-op when the library is up to date
+    return _lib.load()
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(btp_sm100_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    from spear_b200 import _lib
+
+    names = declared_functions()
+    assert len(names) >= 7
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/btp_sm100.h but not exported"
+    assert sorted(_lib.SYMBOLS) == names, "the ctypes prototypes and the header disagree"
+
+
+def test_abi_version_and_status_strings(lib):
+    assert lib.btp_sm100_abi_version() == 1
+    seen = set()
+    for code in range(0, -9, -1):
+        name = lib.btp_sm100_status_string(code).decode()
+        assert name.startswith("BTP_")
+        seen.add(name)
+    assert len(seen) == 9 and "BTP_OK" in seen
+    assert lib.btp_sm100_status_string(-99).decode() == "BTP_ERR_UNKNOWN"
+    text = open(HEADER).read()
+    for name in seen:
+        assert name in text
+
+
+def _fwd(lib, coeff=16, x=16, y=16, ck=0, B=1, H=1, L=16, k=2, cd=0, od=0):
+    p = ctypes.c_void_p
+    return lib.btp_sm100_forward(p(coeff), p(x), p(y), p(ck), B, H, L, k, cd, od, p(0))
+
+
+def _bwd(lib, coeff=16, x=16, dy=16, dx=16, dA=16, B=1, H=1, L=16, k=2, cd=0, dd=0):
+    p = ctypes.c_void_p
+    return lib.btp_sm100_backward(p(coeff), p(x), p(dy), p(0), p(dx), p(dA), B, H, L, k, cd, dd, p(0))
+
+
+def test_argument_errors_come_back_as_codes(lib):
+    """Every check below fires before any CUDA call, so fake (never dereferenced) pointers are fine."""
+    err = lambda: lib.btp_sm100_last_error().decode()
+    assert _fwd(lib, L=24) == -2 and "multiple of 16" in err()       # BTP_ERR_BAD_SHAPE
+    assert _fwd(lib, B=0) == -2
+    assert _fwd(lib, H=-3) == -2
+    assert _fwd(lib, k=3) == -3 and "k must be 1 or 2" in err()      # BTP_ERR_BAD_ORDER
+    assert _fwd(lib, cd=7) == -4                                      # BTP_ERR_BAD_DTYPE
+    assert _fwd(lib, od=2) == -4
+    assert _fwd(lib, x=0) == -1                                       # BTP_ERR_NULL_POINTER
+    assert _fwd(lib, y=8) == -5 and "aligned" in err()                # BTP_ERR_MISALIGNED
+    assert _fwd(lib, ck=4) == -5
+    assert _fwd(lib, B=1 << 20, H=1 << 10, L=16) == -2                # B*H*16 rows beyond int32
+    assert _bwd(lib, L=8) == -2
+    assert _bwd(lib, k=0) == -3
+    assert _bwd(lib, dd=2) == -4
+    assert _bwd(lib, dA=0) == -1
+    assert _bwd(lib, dx=24) == -5
+
+
+def test_no_gpu_is_an_error_not_a_fallback(lib):
+    """With valid arguments and no usable device the call fails with a CUDA error code; nothing is computed."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    rc = _fwd(lib)
+    assert rc in (-6, -7)
+    assert lib.btp_sm100_last_error().decode() != ""
+    assert lib.btp_sm100_launch_count() == 0
+
+
+def test_python_wrapper_has_no_cpu_path():
+    import torch
+
+    from spear_b200.nn.phalanx import Phalanx
+    from spear_b200.ops.btp import btp
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        btp(torch.rand(1, 2, 32), torch.rand(1, 2, 16, 32))
+    for method in ("pytorch", "pytorch_linspace"):
+        with pytest.raises(NotImplementedError):
+            Phalanx(dim=32, method=method)
+    with pytest.raises(ValueError):
+        Phalanx(dim=32, method="triton")
+    with pytest.raises(ValueError):
+        Phalanx(dim=40)            # not divisible by 16 (swr.py:241-242)
+    with pytest.raises(ValueError):
+        Phalanx(dim=64, heads=2)   # head_dim must be 16 (swr.py:247-249)
+    with pytest.raises(ValueError):
+        Phalanx(dim=64, kv_heads=3)

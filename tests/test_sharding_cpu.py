@@ -1,0 +1,91 @@
+"""Batch sharding and the checker's collectives with two gloo ranks on CPU."""
+
+from __future__ import annotations
+
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_shards_cover_the_batch_exactly():
+    from spear_b200.sharding import batch_shard
+
+    for B in (0, 1, 7, 64, 1024, 1025):
+        for world in (1, 2, 3, 4, 8):
+            spans = [batch_shard(B, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == B
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        batch_shard(8, 2, 2)
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import btp_oracle as O
+    from spear_b200.sharding import batch_shard, global_rel_l2, max_over_ranks, sum_over_ranks
+
+    g = torch.Generator().manual_seed(5)
+    B, H, L = 6, 2, 32
+    a = torch.sigmoid(torch.randn(B, H, L, generator=g))
+    x = torch.randn(B, H, 16, L, generator=g)
+    lo, hi = batch_shard(B, rank, world)
+    y_shard = O.btp_forward(a[lo:hi], x[lo:hi])          # every rank computes its own slice only
+    y_full = O.btp_forward(a, x)
+    noisy = y_shard + 1e-3 * (rank + 1)
+    res = {
+        "max": max_over_ranks([1.0 + rank, 5.0 - rank]),
+        "sum": sum_over_ranks([hi - lo]),
+        "rel_exact": global_rel_l2(y_shard, y_full[lo:hi]),
+        "rel_noisy": global_rel_l2(noisy, y_full[lo:hi]),
+    }
+    # reference value of the noisy norm, computed centrally
+    full_noisy = torch.cat([y_full[slice(*batch_shard(B, r, world))] + 1e-3 * (r + 1) for r in range(world)])
+    res["rel_noisy_central"] = O.rel_l2(full_noisy, y_full)
+    if rank == 0:
+        json.dump(res, open(out, "w"))
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks(tmp_path):
+    out = str(tmp_path / "res.json")
+    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = json.load(open(out))
+    assert res["max"] == [2.0, 5.0]
+    assert res["sum"] == [6.0]
+    assert res["rel_exact"] == 0.0
+    assert abs(res["rel_noisy"] - res["rel_noisy_central"]) < 1e-12
+
+
+def test_reference_arm_prints_on_rank_zero_only():
+    """bench.py --impl reference under two ranks: rank 0 prints the one JSON line, rank 1 exits 0 silently."""
+    env = dict(os.environ, WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), OMP_NUM_THREADS="2")
+    outs = []
+    for rank in (0, 1):
+        e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+                            "--steps", "1", "--warmup", "0", "--batch", "8"], env=e, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr
+        outs.append(r.stdout.strip())
+    assert outs[1] == ""
+    line = json.loads(outs[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["cpu_baseline"]["kind"] == "port"
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["value"] > 0
