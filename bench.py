@@ -43,8 +43,9 @@ BWD_BYTES_PER_HT = 102   # coeff 2 + x 32 + dy 32 + dx 32 + dA 4
 NOMINAL_HBM_GBS = 8000.0  # the peak BASELINE.json's north star names
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload
-# (ncu capture summarised in profiles/); None until measured.
-BWD_TRAFFIC_BYTES = None
+# (ncu capture summarised in profiles/btp_fwd_bwd_B1024_H32_L128_ncu_full.md: 276.9 MB read + 116.7 MB written;
+# the remaining 34 MB of the 151 MB of output were still in L2 when the single profiled launch ended).
+BWD_TRAFFIC_BYTES = 393_560_832
 METRIC = "btp_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -319,7 +320,8 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "btp_backward_kernel", "achieved": bwd_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": bwd_gbs / peak, "traffic": BWD_TRAFFIC_BYTES,
+                         "unit": "GB/s", "frac": bwd_gbs / peak,
+                         "traffic": BWD_TRAFFIC_BYTES if (B, H, L) == (1024, 32, 128) else None,
                          "peak_kind": f"of {peak_kind}", "us_per_launch": bwd_us,
                          "algorithmic_bytes_per_launch": BWD_BYTES_PER_HT * ht},
             "roofline_forward": {"bound": "hbm", "kernel": "btp_forward_kernel", "achieved": fwd_gbs, "peak": peak,
