@@ -275,3 +275,76 @@ def test_bad_arguments_raise(native):
     xl = torch.zeros(1, 2, 16, 24, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
         native.forward(a[:, :, :24].contiguous(), xl, torch.empty_like(xl), None, 2, 32)  # L % 16
+
+
+# ------------------------------------------------------------------ public wrapper: autograd, defaults, torch.compile
+def test_btp_wrapper_autograd_and_defaults(native):
+    from spear_b200.ops.btp import btp
+
+    a, x, dy = sample(2, 8, 512, 456)  # shape/seed of tests/btp/test_numerics.py:125-140
+    ad = dev(a, torch.bfloat16).requires_grad_(True)
+    xd = dev(x, torch.bfloat16).requires_grad_(True)
+    y = btp(ad, xd)  # defaults: k=2, output float32 (interface.py:184)
+    assert y.dtype == torch.float32 and y.shape == xd.shape
+    y.backward(dev(dy, torch.float32))
+    assert ad.grad.dtype == torch.bfloat16 and xd.grad.dtype == torch.bfloat16
+    dA_w, dx_w = O.btp_backward(a, x, dy)
+    assert_limits(y.detach().cpu(), O.btp_forward(a, x), FORWARD_LIMITS, "y")
+    assert_limits(xd.grad.float().cpu(), dx_w, BACKWARD_LIMITS, "dx")
+    assert O.rel_l2(ad.grad.float().cpu(), dA_w) <= 1e-2  # after autograd's cast of dA to bf16
+    # non-contiguous inputs are made contiguous like the reference does (interface.py:186-187)
+    xt = dev(x, torch.bfloat16).permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+    assert not xt.is_contiguous()
+    assert torch.equal(btp(ad.detach(), xt), y.detach())
+    with pytest.raises(ValueError):
+        btp(ad.detach()[:, :, :256], xd.detach())
+
+
+def test_btp_traces_under_torch_compile(native):
+    """The mutating custom ops trace as one graph (fullgraph) like the reference's (interface.py:104-120)."""
+    from spear_b200.ops.btp import btp
+
+    a, x, dy = sample(2, 4, 256, 321)
+    ad, xd = dev(a, torch.bfloat16), dev(x, torch.bfloat16)
+    want = btp(ad, xd, output_dtype=torch.bfloat16)
+    fn = torch.compile(btp, fullgraph=True, backend="aot_eager")
+    a2 = ad.clone().requires_grad_(True)
+    x2 = xd.clone().requires_grad_(True)
+    got = fn(a2, x2, output_dtype=torch.bfloat16)
+    assert torch.equal(got, want)
+    got.backward(dev(dy, torch.bfloat16))
+    _, dx_w = O.btp_backward(a, x, dy)
+    assert_limits(x2.grad.float().cpu(), dx_w, BACKWARD_LIMITS, "dx under compile")
+
+
+# ------------------------------------------------------------------ layer: golden outputs of the reference's PyTorch layer
+LAYER_FORWARD_LIMITS = {"max_abs": 1e-1, "rmse": 5e-2}   # tests/phalanx/test_phalanx_numerics.py:41-47
+LAYER_BACKWARD_LIMITS = {"max_abs": 2.2, "rmse": 5e-1}   # tests/phalanx/test_phalanx_numerics.py:49-55
+
+
+@pytest.mark.parametrize("case,kv_heads", [("layer_basic", None), ("layer_kv2", 2)])
+def test_phalanx_layer_matches_reference_layer(native, case, kv_heads):
+    from spear_b200.nn.phalanx import Phalanx
+
+    g = load_golden(case)
+    layer = Phalanx(dim=64, length=48, dtype=torch.bfloat16, kv_heads=kv_heads).cuda()
+    state = {k[2:]: v for k, v in g.items() if k.startswith("w:")}
+    assert set(state) == set(layer.state_dict())  # same parameter names as the reference layer
+    layer.load_state_dict({k: v.to(torch.bfloat16) for k, v in state.items()})
+    u = g["u"].cuda().requires_grad_(True)
+    out = layer(u)
+    assert out.shape == g["out"].shape and out.dtype == torch.bfloat16
+    out.backward(g["dout"].cuda().to(out.dtype))
+    m = O.error_metrics(out.float().cpu(), g["out"])
+    for key, lim in LAYER_FORWARD_LIMITS.items():
+        assert m[key] <= lim, f"layer out {key}={m[key]:.3e}"
+    assert m["rel_l2"] <= 3e-2  # bf16 weights, activations and GEMMs against the fp32 reference layer
+    m = O.error_metrics(u.grad.float().cpu(), g["du"])
+    for key, lim in LAYER_BACKWARD_LIMITS.items():
+        assert m[key] <= lim, f"layer du {key}={m[key]:.3e}"
+    assert m["rel_l2"] <= 5e-2
+    for name, prm in layer.named_parameters():
+        m = O.error_metrics(prm.grad.float().cpu(), g["g:" + name])
+        for key, lim in LAYER_BACKWARD_LIMITS.items():
+            assert m[key] <= lim, f"grad {name} {key}={m[key]:.3e}"
+        assert m["rel_l2"] <= 6e-2, f"grad {name} rel_l2 {m['rel_l2']:.3e}"
