@@ -82,6 +82,9 @@ int device_info(int* dev_out, DeviceInfo* info) {
   int dev = 0;
   BTP_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(BTP_ERR_CUDA, "device ordinal %d out of range", dev);
+  // Binds the device's primary context to the calling thread: the descriptor encoder is a driver entry point
+  // and threads that have made no runtime call yet (autograd's backward thread) have no current context.
+  BTP_CUDA_TRY(cudaSetDevice(dev));
   std::lock_guard<std::mutex> lock(g_dev_mutex);
   if (!g_dev[dev].ready) {
     BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].sms, cudaDevAttrMultiProcessorCount, dev));
