@@ -42,6 +42,7 @@ extern "C" {
 #define BTP_ERR_CUDA (-6)           /* a CUDA runtime / driver call failed; see btp_sm100_last_error() */
 #define BTP_ERR_UNSUPPORTED_DEVICE (-7) /* current device is not compute capability 10.x */
 #define BTP_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel gave up (btp_sm100_device_status) */
+#define BTP_ERR_TOO_LARGE (-9)      /* problem exceeds the built-in scratch of btp_sm100_forward_noalloc */
 
 /* dtype tags */
 #define BTP_DTYPE_BF16 0        /* x, y, dy, dx, coeff */
@@ -75,6 +76,33 @@ int btp_sm100_forward(const void* coeff, const void* x, void* y, float* checkpoi
 int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const float* checkpoint,
                        void* dx, float* dA, int B, int H, int L, int k,
                        int coeff_dtype, int dy_dtype, void* stream);
+
+/*
+ * Forward that also produces the carry checkpoint, but keeps it in memory that is part of the library
+ * image instead of memory the caller has to provide.
+ * No counterpart in the reference (there the Python wrapper allocates the checkpoint with torch.empty,
+ * spear/ops/btp/interface.py:142).
+ *
+ * Who this is for: callers that want the reference's forward behaviour (y plus the per-block carry
+ * record) but are not in a position to allocate device memory for the record at call time - a serving
+ * process whose whole memory budget was handed to an arena at start-up, code running under a framework
+ * allocator it must not bypass, a plugin that only ever receives its input and output buffers.  They pass
+ * coeff, x and y exactly as for btp_sm100_forward and nothing else.
+ *
+ * The record goes to a fixed array of BTP_SM100_NOALLOC_MAX_HEAD_TOKENS floats (4 MiB) that every GPU
+ * holds from the moment it loads the library until the process exits.  The call returns
+ * BTP_ERR_TOO_LARGE when B*H*L exceeds that number; use btp_sm100_forward with your own buffer then.
+ * The entry point itself never calls cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * First call on each device: it looks up the device address of the array (one cudaGetSymbolAddress with
+ * that device current) and keeps it; make this first call outside any stream capture.
+ * The array is shared by all calls and keeps the contents of the last one.  Nothing in it has to start
+ * at zero (every slot that is ever read is written by the same launch), but two calls whose kernels
+ * overlap on the GPU (different streams) write the same slots and race: serialise them.
+ */
+#define BTP_SM100_NOALLOC_MAX_HEAD_TOKENS (1 << 20)
+int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, int H, int L, int k,
+                              int coeff_dtype, int out_dtype, void* stream);
 
 /* Name of a status code ("BTP_OK", "BTP_ERR_BAD_SHAPE", ...).  Never NULL. */
 const char* btp_sm100_status_string(int status);

@@ -280,6 +280,29 @@ int backward_variant(const void* coeff, const void* x, const void* dy, void* dx,
   return launch_backward<COEF, DY_F32, 1, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
 }
 
+// ------------------------------------------------------------------ built-in scratch for btp_sm100_forward_noalloc
+// Lives in the library image: every GPU that loads the library holds these 4 MiB until the process exits.
+// `g_noalloc_ckpt` is only a host-side handle in host code; kernels get the device address that
+// cudaGetSymbolAddress returns for the device that is current.
+static __device__ __align__(256) float g_noalloc_ckpt[BTP_SM100_NOALLOC_MAX_HEAD_TOKENS];
+float* g_noalloc_ckpt_addr[64];
+std::mutex g_noalloc_mutex;
+
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  BTP_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(BTP_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ckpt_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    BTP_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_ckpt));
+    if (ptr == nullptr) return fail(BTP_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the scratch array");
+    g_noalloc_ckpt_addr[dev] = ptr;
+  }
+  *out = g_noalloc_ckpt_addr[dev];
+  return BTP_OK;
+}
+
 }  // namespace
 
 // ====================================================================== C ABI
@@ -330,6 +353,31 @@ int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const f
   }
 }
 
+int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, int H, int L, int k, int coeff_dtype,
+                              int out_dtype, void* stream) {
+  Dims d{};
+  int rc = check_common("btp_sm100_forward_noalloc", B, H, L, k, coeff_dtype, &d);
+  if (rc) return rc;
+  if (out_dtype != BTP_DTYPE_BF16 && out_dtype != BTP_DTYPE_F32)
+    return fail(BTP_ERR_BAD_DTYPE, "btp_sm100_forward_noalloc: unsupported output dtype tag %d", out_dtype);
+  if (!coeff || !x || !y) return fail(BTP_ERR_NULL_POINTER, "btp_sm100_forward_noalloc: coeff, x and y must not be NULL");
+  if (misaligned(coeff) || misaligned(x) || misaligned(y))
+    return fail(BTP_ERR_MISALIGNED, "btp_sm100_forward_noalloc: every pointer must be 16-byte aligned");
+  if (d.BH * L > static_cast<long long>(BTP_SM100_NOALLOC_MAX_HEAD_TOKENS))
+    return fail(BTP_ERR_TOO_LARGE,
+                "btp_sm100_forward_noalloc: B*H*L = %lld exceeds the built-in scratch of %d head-tokens; "
+                "call btp_sm100_forward with a checkpoint buffer of your own",
+                d.BH * L, BTP_SM100_NOALLOC_MAX_HEAD_TOKENS);
+  float* scratch = nullptr;
+  if ((rc = noalloc_scratch(&scratch))) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (coeff_dtype) {
+    case BTP_DTYPE_BF16: return forward_coef<kCoefBf16>(coeff, x, y, scratch, d, k, out_dtype, s);
+    case BTP_DTYPE_F32: return forward_coef<kCoefF32>(coeff, x, y, scratch, d, k, out_dtype, s);
+    default: return forward_coef<kCoefF32Log>(coeff, x, y, scratch, d, k, out_dtype, s);
+  }
+}
+
 const char* btp_sm100_status_string(int status) {
   switch (status) {
     case BTP_OK: return "BTP_OK";
@@ -341,6 +389,7 @@ const char* btp_sm100_status_string(int status) {
     case BTP_ERR_CUDA: return "BTP_ERR_CUDA";
     case BTP_ERR_UNSUPPORTED_DEVICE: return "BTP_ERR_UNSUPPORTED_DEVICE";
     case BTP_ERR_DEVICE_TIMEOUT: return "BTP_ERR_DEVICE_TIMEOUT";
+    case BTP_ERR_TOO_LARGE: return "BTP_ERR_TOO_LARGE";
     default: return "BTP_ERR_UNKNOWN";
   }
 }

@@ -33,7 +33,7 @@ def test_every_declared_symbol_is_exported(lib):
     from spear_b200 import _lib
 
     names = declared_functions()
-    assert len(names) >= 7
+    assert len(names) >= 8
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/btp_sm100.h but not exported"
     assert sorted(_lib.SYMBOLS) == names, "the ctypes prototypes and the header disagree"
@@ -42,11 +42,11 @@ def test_every_declared_symbol_is_exported(lib):
 def test_abi_version_and_status_strings(lib):
     assert lib.btp_sm100_abi_version() == 1
     seen = set()
-    for code in range(0, -9, -1):
+    for code in range(0, -10, -1):
         name = lib.btp_sm100_status_string(code).decode()
         assert name.startswith("BTP_")
         seen.add(name)
-    assert len(seen) == 9 and "BTP_OK" in seen
+    assert len(seen) == 10 and "BTP_OK" in seen
     assert lib.btp_sm100_status_string(-99).decode() == "BTP_ERR_UNKNOWN"
     text = open(HEADER).read()
     for name in seen:
