@@ -121,6 +121,8 @@ def cpu_reference_tokens_per_s(batch: int, reps: int, warm: int):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import btp_oracle as O
 
+    # all the host threads this process may use (torchrun presets OMP_NUM_THREADS=1)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     g = torch.Generator().manual_seed(0)
     a = torch.sigmoid(torch.randn(batch, H, L, generator=g))
     x = torch.randn(batch, H, D, L, generator=g) * 0.25
@@ -139,13 +141,13 @@ def run_reference_arm(args, rank):
     """The reference's CPU path (oracle port) on this box's host cores; rank 0 only."""
     if rank != 0:
         return
-    threads = torch.get_num_threads()
     # size the per-step sample so that the whole run stays within about two minutes
     probe = min(cpu_reference_tokens_per_s(8, 1, 1))
     per_seq = probe / 8
     budget = 120.0 / max(1, args.steps + args.warmup)
     batch = int(max(1, min(B, budget / per_seq)))
     times = cpu_reference_tokens_per_s(batch, args.steps, args.warmup)
+    threads = torch.get_num_threads()
     total = sum(times)
     value = batch * L * len(times) / total
     line = {
