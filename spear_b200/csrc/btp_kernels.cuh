@@ -168,18 +168,27 @@ struct WarpWork {
   }
 };
 
-template <int TL>
+// Blocks in chunk `cs`.  RAGGED == false: L is a multiple of the chunk width, every chunk is full and
+// the count folds to a constant.
+template <int TL, bool RAGGED>
 __device__ __forceinline__ int chunk_tiles(int cs, int L) {
-  const int left = (L - cs * TL) >> 4;
-  return left < TL / 16 ? left : TL / 16;
+  if constexpr (!RAGGED) {
+    return TL / 16;
+  } else {
+    const int left = (L - cs * TL) >> 4;
+    return left < TL / 16 ? left : TL / 16;
+  }
 }
 
 // Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables at `tab`.
 // Lane l owns TPL = TL/32 consecutive tokens; 16/TPL lanes make one block; the prefix sums restart
 // at every block.  Tables (each TL floats): [0] T, then forward [1] P = 2^T,
 // backward [1] Pshift (P of the previous token, 1 for the first token of a block), [2] L15 = 2^(T_15 - T).
+// `carry_scale` is 1 (k = 2) or 0 (k = 1): every use of the carry and of the gradient that flows back
+// through it is multiplied by an entry of the P / Pshift table, so zeroing that table switches the one-hop
+// term off without a single extra instruction per block.
 template <int COEF, int TL, bool BWD>
-__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane) {
+__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane, float carry_scale) {
   constexpr int TPL = TL / 32;    // tokens per lane: 2 or 4
   constexpr int LPT = 16 / TPL;   // lanes per block: 8 or 4
   float v[TPL];
@@ -225,15 +234,15 @@ __device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int l
     const float T15 = __shfl_sync(0xffffffffu, T[TPL - 1], lane | (LPT - 1));
     float prev = __shfl_up_sync(0xffffffffu, P[TPL - 1], 1, LPT);
     if (q == 0) prev = 1.0f;
-    second[0] = prev;
+    second[0] = prev * carry_scale;
 #pragma unroll
-    for (int k = 1; k < TPL; ++k) second[k] = P[k - 1];
+    for (int k = 1; k < TPL; ++k) second[k] = P[k - 1] * carry_scale;
 #pragma unroll
     for (int k = 0; k < TPL; ++k) third[k] = ex2(T15 - T[k]);
   } else {
 #pragma unroll
     for (int k = 0; k < TPL; ++k) {
-      second[k] = P[k];
+      second[k] = P[k] * carry_scale;
       third[k] = 0.0f;
     }
   }
@@ -385,7 +394,7 @@ __device__ __forceinline__ void report_error(unsigned int code, int warp, int ch
 // =====================================================================================
 // Forward
 // =====================================================================================
-template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const KernelParams p) {
@@ -426,11 +435,12 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   __syncwarp();
 
   const int L = p.L, ncs = p.ncs;
+  const float carry_scale = p.use_carry ? 1.0f : 0.0f;
   ChunkCursor prod(work.bh, work.cs, work.step), cons(work.bh, work.cs, work.step);
   int s_prod = 0;
   auto issue = [&]() {  // starts the loads of the producer cursor's chunk into stage s_prod, then advances
     if (lane == 0) {
-      const int nt = chunk_tiles<TL>(prod.cs, L);
+      const int nt = chunk_tiles<TL, RAGGED>(prod.cs, L);
       const int c0 = prod.cs * TL;
       const int nbox = (nt + 3) >> 2;
       const uint32_t cbytes = nt * 16 * kEsz;
@@ -462,10 +472,10 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       failed = true;
       break;
     }
-    const int nt = chunk_tiles<TL>(cons.cs, L);
+    const int nt = chunk_tiles<TL, RAGGED>(cons.cs, L);
     const int c0 = cons.cs * TL;
     float* tab = ws.tab_ptr(0);
-    chunk_tables<COEF, TL, false>(ws.raw_ptr(s), tab, lane);
+    chunk_tables<COEF, TL, false>(ws.raw_ptr(s), tab, lane, carry_scale);
 
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
@@ -511,11 +521,9 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             ck[16 * i + 8] = v1[3];
           }
         }
-        if (p.use_carry) {
-          // carry for the next block: the UNCORRECTED last token (btp-forward.cu:297-299)
-          cg = __shfl_sync(0xffffffffu, v1[1], lane | 3);
-          cg8 = __shfl_sync(0xffffffffu, v1[3], lane | 3);
-        }
+        // carry for the next block: the UNCORRECTED last token (btp-forward.cu:297-299)
+        cg = __shfl_sync(0xffffffffu, v1[1], lane | 3);
+        cg8 = __shfl_sync(0xffffffffu, v1[3], lane | 3);
         if constexpr (OUT_F32) {
           const long long r8 = 8ll * L;
           *reinterpret_cast<float2*>(yo + 16 * i) = make_float2(y0[0], y0[1]);
@@ -573,7 +581,7 @@ struct TileAcc {
   float g0[4], g1[4];  // gw = dy . Lmat
 };
 
-template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool DY_F32, bool RAGGED, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                     const __grid_constant__ CUtensorMap tm_dx, const KernelParams p) {
@@ -611,11 +619,12 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   __syncwarp();
 
   const int L = p.L, ncs = p.ncs;
+  const float carry_scale = p.use_carry ? 1.0f : 0.0f;
   ChunkCursor prod(work.bh, work.cs, work.step), cons(work.bh, work.cs, work.step);
   int s_prod = 0, d_prod = 0, issued = 0;
   auto issue = [&]() {
     if (lane == 0) {
-      const int nt = chunk_tiles<TL>(prod.cs, L);
+      const int nt = chunk_tiles<TL, RAGGED>(prod.cs, L);
       const int c0 = prod.cs * TL;
       const int nbox = (nt + 3) >> 2;
       const int nbox_dy = DY_F32 ? (nt + 1) >> 1 : nbox;
@@ -773,10 +782,10 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       failed = true;
       break;
     }
-    const int nt = chunk_tiles<TL>(cons.cs, L);
+    const int nt = chunk_tiles<TL, RAGGED>(cons.cs, L);
     const int c0 = cons.cs * TL;
     float* tab = ws.tab_ptr(tset);
-    chunk_tables<COEF, TL, true>(ws.raw_ptr(s), tab, lane);
+    chunk_tables<COEF, TL, true>(ws.raw_ptr(s), tab, lane, carry_scale);
     if (j == 0 && cons.cs != 0 && p.use_carry) {
       halo_reduce<COEF, false, false>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
     }
@@ -788,7 +797,6 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const uint32_t ldm = xs + tl.ldm_base;
     const uint32_t stb = xs + tl.st_base;
     const bool seq_first = (cons.cs == 0);
-    const bool carry_on = p.use_carry != 0;
 
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
@@ -797,9 +805,8 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const TileAcc& prev = (i & 1) ? accA : accB;  // block i-1 (slot B holds the pending one when i == 0)
         float dc_g, dc_g8;
         front(tab, tg, tt, ldm, dys, i, cur, dc_g, dc_g8);
-        if (!carry_on) dc_g = dc_g8 = 0.0f;
-        const float ncg = ((i == 0 && seq_first) || !carry_on) ? 0.0f : vl_g;  // carry into block i
-        const float ncg8 = ((i == 0 && seq_first) || !carry_on) ? 0.0f : vl_g8;
+        const float ncg = (i == 0 && seq_first) ? 0.0f : vl_g;  // carry into block i
+        const float ncg8 = (i == 0 && seq_first) ? 0.0f : vl_g8;
         if (i == 0) {
           if (have) {
             back(prev, p_tt, p_da, p_o0, p_cg, p_cg8, p_seq_end ? 0.0f : dc_g, p_seq_end ? 0.0f : dc_g8);

@@ -181,10 +181,10 @@ bool use_interleave(const Dims& d, long long nwarps) {
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 // ------------------------------------------------------------------ forward dispatch
-template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
-int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, int NBOX, int STAGES, int WARPS>
+int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
-  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, NBOX, STAGES, WARPS>;
+  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, RAGGED, NBOX, STAGES, WARPS>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
   DeviceInfo info;
@@ -209,6 +209,13 @@ int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims 
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
+}
+
+// Sequences that are a whole number of chunks get the kernel without ragged-chunk handling.
+template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
+int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
+  if (d.L % (64 * NBOX) == 0) return launch_forward_impl<COEF, OUT_F32, CKPT, false, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  return launch_forward_impl<COEF, OUT_F32, CKPT, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
 }
 
 template <int COEF, bool OUT_F32, bool CKPT>
@@ -237,11 +244,11 @@ int forward_coef(const void* coeff, const void* x, void* y, float* ckpt, Dims d,
 }
 
 // ------------------------------------------------------------------ backward dispatch
-template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
-int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
-                    cudaStream_t stream) {
+template <int COEF, bool DY_F32, bool RAGGED, int NBOX, int STAGES, int WARPS>
+int launch_backward_impl(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
+                         cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, true, DY_F32>;
-  auto kern = btp_backward_kernel<COEF, DY_F32, NBOX, STAGES, WARPS>;
+  auto kern = btp_backward_kernel<COEF, DY_F32, RAGGED, NBOX, STAGES, WARPS>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
   DeviceInfo info;
@@ -263,6 +270,13 @@ int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, 
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
+}
+
+template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
+int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
+                    cudaStream_t stream) {
+  if (d.L % (64 * NBOX) == 0) return launch_backward_impl<COEF, DY_F32, false, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  return launch_backward_impl<COEF, DY_F32, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
 }
 
 template <int COEF, bool DY_F32>
