@@ -383,6 +383,28 @@ __device__ __forceinline__ LmatFrag build_lmat(const float* tg, const float* tt,
 }
 
 // code 1: a bounded wait gave up; code 2: shared-memory base not 1024-byte aligned
+// The same fragments split into two bf16 terms, Lmat = hi + lo with |lo| <= 2^-9 |hi|: feeding both to the
+// tensor cores reproduces the fp32 Lmat to about 2^-17 instead of 2^-9.
+__device__ __forceinline__ void build_lmat_split(const float* tg, const float* tt, int off, const TileLane& tl,
+                                                 LmatFrag& hi, LmatFrag& lo) {
+  const float Tg = tg[off];
+  const float Tg8 = tg[off + 8];
+  const float2 Ta = *reinterpret_cast<const float2*>(tt + off);
+  const float2 Tb = *reinterpret_cast<const float2*>(tt + off + 8);
+  const float e0 = tl.m0 ? ex2(Tg - Ta.x) : 0.0f;
+  const float e1 = tl.m1 ? ex2(Tg - Ta.y) : 0.0f;
+  const float e2 = ex2(Tg8 - Ta.x);
+  const float e3 = ex2(Tg8 - Ta.y);
+  const float e4 = tl.m0 ? ex2(Tg8 - Tb.x) : 0.0f;
+  const float e5 = tl.m1 ? ex2(Tg8 - Tb.y) : 0.0f;
+  hi.b00 = pack_bf16x2(e0, e1);
+  hi.b10 = pack_bf16x2(e2, e3);
+  hi.b11 = pack_bf16x2(e4, e5);
+  lo.b00 = pack_bf16x2(e0 - bf16_lo(hi.b00), e1 - bf16_hi(hi.b00));
+  lo.b10 = pack_bf16x2(e2 - bf16_lo(hi.b10), e3 - bf16_hi(hi.b10));
+  lo.b11 = pack_bf16x2(e4 - bf16_lo(hi.b11), e5 - bf16_hi(hi.b11));
+}
+
 __device__ __forceinline__ void report_error(unsigned int code, int warp, int chunk) {
   if (atomicCAS(&g_btp_device_error[0], 0u, code) == 0u) {
     g_btp_device_error[1] = blockIdx.x;
@@ -394,7 +416,8 @@ __device__ __forceinline__ void report_error(unsigned int code, int warp, int ch
 // =====================================================================================
 // Forward
 // =====================================================================================
-template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, int NBOX, int STAGES, int WARPS>
+// PRECISE: Lmat goes to the tensor cores as two bf16 terms (see build_lmat_split).
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const KernelParams p) {
@@ -501,12 +524,21 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     for (int i = 0; i < NT; ++i) {
       if (i < nt) {
         const int box = i >> 2, ib = i & 3;
-        const LmatFrag lf = build_lmat(tg, tt, 16 * i, tl);
+        LmatFrag lf, lo;
+        if constexpr (PRECISE) {
+          build_lmat_split(tg, tt, 16 * i, tl, lf, lo);
+        } else {
+          lf = build_lmat(tg, tt, 16 * i, tl);
+        }
         uint32_t a0, a1, a2, a3;
         ldmatrix_x4(ldm + box * 2048 + tl.ldm_off[ib], a0, a1, a2, a3);
         float v0[4], v1[4];
         mma_1688(v0, a0, a1, lf.b00);
         mma_16816(v1, a0, a1, a2, a3, lf.b10, lf.b11);
+        if constexpr (PRECISE) {
+          mma_1688_acc(v0, a0, a1, lo.b00);
+          mma_16816_acc(v1, a0, a1, a2, a3, lo.b10, lo.b11);
+        }
         const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
         const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);
         float y0[4], y1[4];
@@ -581,7 +613,9 @@ struct TileAcc {
   float g0[4], g1[4];  // gw = dy . Lmat
 };
 
-template <int COEF, bool DY_F32, bool RAGGED, int NBOX, int STAGES, int WARPS>
+// PRECISE: the Lmat operand goes to the tensor cores as two bf16 terms (4 more products per block), which
+// brings dA to the accuracy of a float32 evaluation; without it Lmat is rounded to bf16 once.
+template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                     const __grid_constant__ CUtensorMap tm_dx, const KernelParams p) {
@@ -656,7 +690,12 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   auto front = [&](const float* tab, const float* tg, const float* tt, uint32_t ldm_x, uint32_t dy_s, int i,
                    TileAcc& acc, float& dc_g, float& dc_g8) {  // dy_s: the chunk's dy buffer
     const int box = i >> 2, ib = i & 3;
-    const LmatFrag lf = build_lmat(tg, tt, 16 * i, tl);
+    LmatFrag lf, lo;
+    if constexpr (PRECISE) {
+      build_lmat_split(tg, tt, 16 * i, tl, lf, lo);
+    } else {
+      lf = build_lmat(tg, tt, 16 * i, tl);
+    }
     // dy . Lmat needs the transposed 8x8 blocks as B operand (k = r, n = c)
     const uint32_t g00 = movmatrix_trans(lf.b00);
     const uint32_t g10 = movmatrix_trans(lf.b10);
@@ -685,6 +724,12 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     mma_16816(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
     mma_16816(acc.g0, e0, e1, e2, e3, g00, g10);
     mma_1688(acc.g1, e2, e3, g11);
+    if constexpr (PRECISE) {
+      mma_1688_acc(acc.v0, a0, a1, lo.b00);
+      mma_16816_acc(acc.v1, a0, a1, a2, a3, lo.b10, lo.b11);
+      mma_16816_acc(acc.g0, e0, e1, e2, e3, movmatrix_trans(lo.b00), movmatrix_trans(lo.b10));
+      mma_1688_acc(acc.g1, e2, e3, movmatrix_trans(lo.b11));
+    }
     // gradient this block sends to its left neighbour: P[0] * gw[:,0]   (P[0] = Pshift[1])
     const float a_first = tab[TL + 16 * i + 1];
     dc_g = a_first * __shfl_sync(0xffffffffu, acc.g0[0], lane & ~3);

@@ -141,6 +141,24 @@ int variant() {
   return v;
 }
 
+// Backward with the Lmat operand split into two bf16 terms (BTP_SM100_PRECISE_BWD=0 selects the single-term
+// kernel, which is about a tenth faster and leaves dA at the accuracy of a bf16 Lmat).
+bool precise_backward() {
+  static const bool v = [] {
+    const char* e = getenv("BTP_SM100_PRECISE_BWD");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return v;
+}
+
+bool precise_forward() {
+  static const bool v = [] {
+    const char* e = getenv("BTP_SM100_PRECISE_FWD");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return v;
+}
+
 struct Dims {
   int B, H, L;
   long long BH;
@@ -181,10 +199,10 @@ bool use_interleave(const Dims& d, long long nwarps) {
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 // ------------------------------------------------------------------ forward dispatch
-template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
 int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
-  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, RAGGED, NBOX, STAGES, WARPS>;
+  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, RAGGED, PRECISE, NBOX, STAGES, WARPS>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
   DeviceInfo info;
@@ -214,8 +232,13 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
 // Sequences that are a whole number of chunks get the kernel without ragged-chunk handling.
 template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
 int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
-  if (d.L % (64 * NBOX) == 0) return launch_forward_impl<COEF, OUT_F32, CKPT, false, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
-  return launch_forward_impl<COEF, OUT_F32, CKPT, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  const bool ragged = d.L % (64 * NBOX) != 0;
+  if (precise_forward()) {
+    if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+    return launch_forward_impl<COEF, OUT_F32, CKPT, true, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  }
+  if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, false, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  return launch_forward_impl<COEF, OUT_F32, CKPT, true, false, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
 }
 
 template <int COEF, bool OUT_F32, bool CKPT>
@@ -244,11 +267,11 @@ int forward_coef(const void* coeff, const void* x, void* y, float* ckpt, Dims d,
 }
 
 // ------------------------------------------------------------------ backward dispatch
-template <int COEF, bool DY_F32, bool RAGGED, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
 int launch_backward_impl(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
                          cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, true, DY_F32>;
-  auto kern = btp_backward_kernel<COEF, DY_F32, RAGGED, NBOX, STAGES, WARPS>;
+  auto kern = btp_backward_kernel<COEF, DY_F32, RAGGED, PRECISE, NBOX, STAGES, WARPS>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
   DeviceInfo info;
@@ -275,8 +298,13 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
 template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
 int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
                     cudaStream_t stream) {
-  if (d.L % (64 * NBOX) == 0) return launch_backward_impl<COEF, DY_F32, false, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
-  return launch_backward_impl<COEF, DY_F32, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  const bool ragged = d.L % (64 * NBOX) != 0;
+  if (precise_backward()) {
+    if (!ragged) return launch_backward_impl<COEF, DY_F32, false, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+    return launch_backward_impl<COEF, DY_F32, true, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  }
+  if (!ragged) return launch_backward_impl<COEF, DY_F32, false, false, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  return launch_backward_impl<COEF, DY_F32, true, false, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
 }
 
 template <int COEF, bool DY_F32>
