@@ -33,6 +33,35 @@ def _require(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
+try:  # the raw-stream lookup that compiled launchers use; a few hundred ns instead of a Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:  # pragma: no cover
+    def _raw_stream(index: int) -> int:
+        return torch.cuda.current_stream(index).cuda_stream
+
+
+class _OnDevice:
+    """Makes `index` the current CUDA device for the call, only if it is not already."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+        return _raw_stream(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None or t.numel() == 0 else t.data_ptr())
 
@@ -62,8 +91,7 @@ def forward(coeff, x, y, checkpoint, k: int, wpb: int, *, log_coeff: bool = Fals
         _require(tuple(checkpoint.shape) == (B, H, L // BLK, DH), "checkpoint must be [B, H, L/16, 16]")
     ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
     _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
-    with torch.cuda.device(x.device):
-        stream = torch.cuda.current_stream().cuda_stream
+    with _OnDevice(x.device.index) as stream:
         rc = _lib.load().btp_sm100_forward(
             _ptr(coeff), _ptr(x), _ptr(y), _ptr(checkpoint), B, H, L, int(k), ctag, _TAG[y.dtype], ctypes.c_void_p(stream)
         )
@@ -79,8 +107,7 @@ def backward(coeff, x, dy, checkpoint, dx, dA, k: int, wpb: int, *, log_coeff: b
     _require(tuple(dA.shape) == (B, H, L) and dA.dtype == torch.float32 and dA.is_contiguous(), "dA must be float32 [B, H, L]")
     ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
     _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
-    with torch.cuda.device(x.device):
-        stream = torch.cuda.current_stream().cuda_stream
+    with _OnDevice(x.device.index) as stream:
         rc = _lib.load().btp_sm100_backward(
             _ptr(coeff), _ptr(x), _ptr(dy), _ptr(None), _ptr(dx), _ptr(dA), B, H, L, int(k), ctag, _TAG[dy.dtype],
             ctypes.c_void_p(stream),

@@ -180,39 +180,21 @@ __device__ __forceinline__ int chunk_tiles(int cs, int L) {
   }
 }
 
-// Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables at `tab`.
-// Lane l owns TPL = TL/32 consecutive tokens; 16/TPL lanes make one block; the prefix sums restart
-// at every block.  Tables (each TL floats): [0] T, then forward [1] P = 2^T,
+// Tables of one chunk from the log2 of its coefficients, held in registers: lane l owns TPL = TL/32
+// consecutive tokens, 16/TPL lanes make one block, the prefix sums restart at every block.
+// Tables (each TL floats): [0] T, then forward [1] P = 2^T,
 // backward [1] Pshift (P of the previous token, 1 for the first token of a block), [2] L15 = 2^(T_15 - T).
 // `carry_scale` is 1 (k = 2) or 0 (k = 1): every use of the carry and of the gradient that flows back
 // through it is multiplied by an entry of the P / Pshift table, so zeroing that table switches the one-hop
 // term off without a single extra instruction per block.
-template <int COEF, int TL, bool BWD>
-__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane, float carry_scale) {
+template <int TL, bool BWD>
+__device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], float* tab, int lane, float carry_scale) {
   constexpr int TPL = TL / 32;    // tokens per lane: 2 or 4
   constexpr int LPT = 16 / TPL;   // lanes per block: 8 or 4
-  float v[TPL];
-  if constexpr (COEF == kCoefBf16) {
-    if constexpr (TPL == 4) {
-      const uint2 raw = reinterpret_cast<const uint2*>(rawp)[lane];
-      v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
-    } else {
-      const uint32_t raw = reinterpret_cast<const uint32_t*>(rawp)[lane];
-      v[0] = bf16_lo(raw); v[1] = bf16_hi(raw);
-    }
-  } else {
-    if constexpr (TPL == 4) {
-      const float4 raw = reinterpret_cast<const float4*>(rawp)[lane];
-      v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
-    } else {
-      const float2 raw = reinterpret_cast<const float2*>(rawp)[lane];
-      v[0] = raw.x; v[1] = raw.y;
-    }
-  }
   float T[TPL];
-  T[0] = coef_log2<COEF>(v[0]);
+  T[0] = l2[0];
 #pragma unroll
-  for (int k = 1; k < TPL; ++k) T[k] = T[k - 1] + coef_log2<COEF>(v[k]);
+  for (int k = 1; k < TPL; ++k) T[k] = T[k - 1] + l2[k];
   // exclusive prefix of the lane totals inside the block
   const int q = lane & (LPT - 1);
   float inc = T[TPL - 1];
@@ -257,6 +239,34 @@ __device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int l
     if constexpr (BWD) reinterpret_cast<float2*>(tab + 2 * TL)[lane] = make_float2(third[0], third[1]);
   }
   __syncwarp();
+}
+
+// Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables at `tab`.
+template <int COEF, int TL, bool BWD>
+__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane, float carry_scale) {
+  constexpr int TPL = TL / 32;  // tokens per lane: 2 or 4
+  float v[TPL];
+  if constexpr (COEF == kCoefBf16) {
+    if constexpr (TPL == 4) {
+      const uint2 raw = reinterpret_cast<const uint2*>(rawp)[lane];
+      v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
+    } else {
+      const uint32_t raw = reinterpret_cast<const uint32_t*>(rawp)[lane];
+      v[0] = bf16_lo(raw); v[1] = bf16_hi(raw);
+    }
+  } else {
+    if constexpr (TPL == 4) {
+      const float4 raw = reinterpret_cast<const float4*>(rawp)[lane];
+      v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+    } else {
+      const float2 raw = reinterpret_cast<const float2*>(rawp)[lane];
+      v[0] = raw.x; v[1] = raw.y;
+    }
+  }
+  float l2[TPL];
+#pragma unroll
+  for (int k = 0; k < TPL; ++k) l2[k] = coef_log2<COEF>(v[k]);
+  tables_from_log2<TL, BWD>(l2, tab, lane, carry_scale);
 }
 
 // Halo: a 16x16 block that belongs to a neighbouring warp's range is read straight from global
