@@ -104,6 +104,22 @@ int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const f
 int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, int H, int L, int k,
                               int coeff_dtype, int out_dtype, void* stream);
 
+/*
+ * Gated forward in token-major layout: the Phalanx layer's glue fused around the op.
+ * Replaces, in one kernel, spear/nn/phalanx/swr.py:216-219 (a = sigmoid(A_logits), X = sigmoid(B_logits) * V),
+ * the two transposing copies of spear/ops/btp/interface.py:186-187, spear._btp.forward, and
+ * swr.py:320-323 (y * C + V and the permute back to [B, L, H*16]).
+ *   a_logits  [B, L, H]      bf16, row pitch ld_a elements (>= H)
+ *   b_logits  [B, L, H*16]   bf16, row pitch ld_b   \  pitches are multiples of 8 elements, bases 16-byte aligned;
+ *   c, v      [B, L, H*16]   bf16, pitches ld_c, ld_v } the four inputs may be column slices of one wide
+ *   out       [B, L, H*16]   bf16, pitch ld_out      /  projection output
+ *   H % 4 == 0, L % 16 == 0, k as in btp_sm100_forward.
+ * out = btp(sigmoid(a_logits), sigmoid(b_logits) * v) * c + v, with the decay rounded to bf16 as the layer does.
+ */
+int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out,
+                            int B, int L, int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
+                            long long ld_out, int k, void* stream);
+
 /* Name of a status code ("BTP_OK", "BTP_ERR_BAD_SHAPE", ...).  Never NULL. */
 const char* btp_sm100_status_string(int status);
 

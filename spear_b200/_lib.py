@@ -22,11 +22,12 @@ DTYPE_F32_LOG = 2
 ABI_VERSION = 1
 
 # every symbol include/btp_sm100.h declares: name -> (restype, argtypes)
-_vp, _i = ctypes.c_void_p, ctypes.c_int
+_vp, _i, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 SYMBOLS = {
     "btp_sm100_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_forward_noalloc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "btp_sm100_gated_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _vp]),
     "btp_sm100_status_string": (ctypes.c_char_p, [_i]),
     "btp_sm100_last_error": (ctypes.c_char_p, []),
     "btp_sm100_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_uint)]),

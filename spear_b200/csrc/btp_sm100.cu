@@ -10,6 +10,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "btp_gated.cuh"
 #include "btp_kernels.cuh"
 
 namespace {
@@ -64,6 +65,21 @@ int make_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L
   const CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return BTP_OK;
+}
+
+// Token-major tensor [B][L][cols] bf16 with row pitch `ld` elements; box = 64 tokens x 64 channels.
+int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, long long ld) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(ld) * 2 * L};
+  const cuuint32_t box[3] = {64u, 64u, 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
   return BTP_OK;
@@ -418,6 +434,57 @@ int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, 
     case BTP_DTYPE_F32: return forward_coef<kCoefF32>(coeff, x, y, scratch, d, k, out_dtype, s);
     default: return forward_coef<kCoefF32Log>(coeff, x, y, scratch, d, k, out_dtype, s);
   }
+}
+
+int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out, int B,
+                            int L, int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
+                            long long ld_out, int k, void* stream) {
+  const char* fn = "btp_sm100_gated_forward";
+  if (B <= 0 || H <= 0 || L <= 0) return fail(BTP_ERR_BAD_SHAPE, "%s: B, L, H must be positive (got %d, %d, %d)", fn, B, L, H);
+  if (L % 16 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: L must be a multiple of 16 (got %d)", fn, L);
+  if (H % 4 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: the number of heads must be a multiple of 4 (got %d)", fn, H);
+  if (k != 1 && k != 2) return fail(BTP_ERR_BAD_ORDER, "%s: k must be 1 or 2 (got %d)", fn, k);
+  if (!a_logits || !b_logits || !c || !v || !out) return fail(BTP_ERR_NULL_POINTER, "%s: no pointer may be NULL", fn);
+  const long long cols = static_cast<long long>(H) * 16;
+  if (ld_a < H || ld_b < cols || ld_c < cols || ld_v < cols || ld_out < cols)
+    return fail(BTP_ERR_BAD_SHAPE, "%s: a row pitch is smaller than its row", fn);
+  if (ld_b % 8 || ld_c % 8 || ld_v % 8 || ld_out % 8)
+    return fail(BTP_ERR_MISALIGNED, "%s: row pitches of B_logits, C, V and out must be multiples of 8 elements", fn);
+  if (misaligned(b_logits) || misaligned(c) || misaligned(v) || misaligned(out) || (reinterpret_cast<uintptr_t>(a_logits) & 1u))
+    return fail(BTP_ERR_MISALIGNED, "%s: B_logits, C, V and out must be 16-byte aligned", fn);
+  const int hgs = H / 4;
+  const int ncs = (L + kGatedTL - 1) / kGatedTL;
+  const long long total = static_cast<long long>(B) * hgs * ncs;
+  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
+  constexpr int STAGES = 3;
+  using SM = GatedSmem<STAGES>;
+  auto kern = btp_gated_forward_kernel<STAGES>;
+  static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = LN.prepare(dev, &ctas))) return rc;
+  CUtensorMap tm_b, tm_c, tm_v, tm_o;
+  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, static_cast<int>(cols), ld_b))) return rc;
+  if ((rc = make_map_tokens(&tm_c, c, B, L, static_cast<int>(cols), ld_c))) return rc;
+  if ((rc = make_map_tokens(&tm_v, v, B, L, static_cast<int>(cols), ld_v))) return rc;
+  if ((rc = make_map_tokens(&tm_o, out, B, L, static_cast<int>(cols), ld_out))) return rc;
+  const long long cap = static_cast<long long>(info.sms) * ctas;
+  const int grid = static_cast<int>(total < cap ? total : cap);
+  GatedParams p{};
+  p.a_logits = static_cast<const __nv_bfloat16*>(a_logits);
+  p.b_logits = static_cast<const __nv_bfloat16*>(b_logits);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.ld_a = ld_a; p.ld_b = ld_b; p.ld_v = ld_v;
+  p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
+  p.use_carry = (k == 2);
+  p.interleave = (ncs <= 8) && (static_cast<long long>(B) * hgs >= 4ll * grid);
+  kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_o, p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
 }
 
 const char* btp_sm100_status_string(int status) {

@@ -157,8 +157,24 @@ class Phalanx(nn.Module):
 
         self.btp_module = btp
         self._forward_fn = self._forward_default
+        # The gating around the op runs fused, in the projections' own token-major layout, whenever the kernel
+        # supports the configuration; set to False for the reference's operation-by-operation data flow.
+        self.fused_gating = True
+
+    def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
+        from spear_b200.ops.btp.gated import gated_btp
+
+        u = x.to(self.compute_dtype)
+        prm = self.param
+        y = gated_btp(prm.proj_a(u), prm.proj_b(u), prm.proj_c(u), prm.proj_v(u), self.k)
+        return self.proj_out(y)
 
     def _forward_default(self, x: torch.Tensor) -> torch.Tensor:
+        from spear_b200.ops.btp.gated import gated_btp_supported
+
+        if (self.fused_gating and x.is_cuda and self.output_dtype == torch.bfloat16 and self.dtype == torch.bfloat16
+                and gated_btp_supported(self.heads, self.kv_heads, x.shape[1])):
+            return self._forward_fused(x)
         A, X, C, V = self.param.forward_axcv(x)
         y = self.btp_module(A, X, self.k, self.wpb, self.output_dtype)
         y = y * C + V

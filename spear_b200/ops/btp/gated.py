@@ -1,0 +1,107 @@
+"""Gated BTP in token-major layout: the Phalanx layer's glue fused around the op.
+
+    out = btp(sigmoid(A_logits), sigmoid(B_logits) * V) * C + V
+
+with every tensor laid out as the layer's projections produce it ([B, L, H] and [B, L, H*16]); replaces
+spear/nn/phalanx/swr.py:216-219 and 320-323 plus the two transposing copies of
+spear/ops/btp/interface.py:186-187.  CUDA only, bf16 only, no fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ... import _btp as _native
+from ... import _lib
+
+__all__ = ["gated_btp", "gated_btp_supported"]
+
+
+def gated_btp_supported(heads: int, kv_heads: int, length: int) -> bool:
+    """The fused kernels take 4 heads per CTA and one key/value head per head."""
+    return heads % 4 == 0 and kv_heads == heads and length % 16 == 0
+
+
+def _rows(t: torch.Tensor, cols: int, what: str) -> int:
+    """Row pitch (elements) of a [B, L, cols] tensor whose rows are dense and evenly spaced."""
+    if t.dim() != 3 or t.shape[2] != cols:
+        raise ValueError(f"{what} must be [B, L, {cols}], got {tuple(t.shape)}")
+    if t.dtype != torch.bfloat16 or not t.is_cuda:
+        raise RuntimeError(f"{what} must be a CUDA bfloat16 tensor (there is no CPU path)")
+    B, L, _ = t.shape
+    if t.stride(2) != 1 or (B > 1 and t.stride(0) != L * t.stride(1)):
+        raise ValueError(f"{what}: rows must be dense and evenly spaced (strides {t.stride()})")
+    return t.stride(1)
+
+
+def _forward_impl(a_logits, b_logits, c, v, out, k: int) -> None:
+    B, L, H = a_logits.shape
+    cols = H * 16
+    ld_a = _rows(a_logits, H, "a_logits")
+    ld_b, ld_c, ld_v, ld_o = (_rows(t, cols, n) for t, n in ((b_logits, "b_logits"), (c, "c"), (v, "v"), (out, "out")))
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    with _native._OnDevice(v.device.index) as stream:
+        rc = _lib.load().btp_sm100_gated_forward(p(a_logits), p(b_logits), p(c), p(v), p(out), B, L, H, ld_a, ld_b, ld_c,
+                                                 ld_v, ld_o, int(k), ctypes.c_void_p(stream))
+    _lib.check(rc, "btp_sm100_gated_forward")
+
+
+def _to_heads(t: torch.Tensor, H: int) -> torch.Tensor:
+    """[B, L, H*16] -> contiguous [B, H, 16, L]"""
+    B, L, _ = t.shape
+    return t.reshape(B, L, H, 16).permute(0, 2, 3, 1).contiguous()
+
+
+def _to_tokens(t: torch.Tensor) -> torch.Tensor:
+    """[B, H, 16, L] -> [B, L, H*16]"""
+    B, H, D, L = t.shape
+    return t.permute(0, 3, 1, 2).reshape(B, L, H * D)
+
+
+class _GatedBTP(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a_logits, b_logits, c, v, k):
+        out = torch.empty(v.shape, device=v.device, dtype=v.dtype)
+        _forward_impl(a_logits, b_logits, c, v, out, k)
+        ctx.save_for_backward(a_logits, b_logits, c, v)
+        ctx.k = int(k)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        # Unfused for now: the op's own backward kernel between elementwise CUDA passes.
+        a_logits, b_logits, c, v = ctx.saved_tensors
+        B, L, H = a_logits.shape
+        a = torch.sigmoid(a_logits).transpose(1, 2).contiguous()
+        sb = torch.sigmoid(b_logits)
+        x = _to_heads(sb * v, H)
+        y = torch.empty_like(x)
+        _native.forward(a, x, y, None, ctx.k, 32)
+        dout = dout.contiguous()
+        dy = _to_heads(dout * c, H)
+        dx = torch.empty_like(x)
+        dA = torch.empty(a.shape, device=a.device, dtype=torch.float32)
+        _native.backward(a, x, dy, None, dx, dA, ctx.k, 32)
+        dx_t = _to_tokens(dx)
+        dc = dout * _to_tokens(y)
+        dv = dout + dx_t * sb
+        db = dx_t * v * (sb * (1 - sb))
+        af = a.float()
+        da_logits = (dA * af * (1 - af)).transpose(1, 2).to(a_logits.dtype)
+        return da_logits, db, dc, dv, None
+
+
+def gated_btp(a_logits: torch.Tensor, b_logits: torch.Tensor, c: torch.Tensor, v: torch.Tensor, k: int = 2) -> torch.Tensor:
+    """out[B, L, H*16] = btp(sigmoid(a_logits), sigmoid(b_logits) * v) * c + v, token-major throughout.
+
+    a_logits: [B, L, H]; b_logits, c, v: [B, L, H*16]; all CUDA bfloat16 with dense rows (they may be column
+    slices of one wider projection output).  H must be a multiple of 4 and L a multiple of 16.
+    """
+    if a_logits.dim() != 3:
+        raise ValueError("a_logits must be [B, L, H]")
+    H = a_logits.shape[2]
+    if not gated_btp_supported(H, H, a_logits.shape[1]):
+        raise ValueError(f"gated_btp needs heads % 4 == 0 and L % 16 == 0 (got H={H}, L={a_logits.shape[1]})")
+    return _GatedBTP.apply(a_logits, b_logits, c, v, k)

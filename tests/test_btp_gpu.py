@@ -348,3 +348,60 @@ def test_phalanx_layer_matches_reference_layer(native, case, kv_heads):
         for key, lim in LAYER_BACKWARD_LIMITS.items():
             assert m[key] <= lim, f"grad {name} {key}={m[key]:.3e}"
         assert m["rel_l2"] <= 6e-2, f"grad {name} rel_l2 {m['rel_l2']:.3e}"
+
+
+# ------------------------------------------------------------------ gated op in token-major layout (the layer's glue, fused)
+def _gated_oracle(a_logits, b_logits, c, v, k=2):
+    """The layer's data flow in float32 on CPU around the oracle op; the decay is rounded to bf16 as the
+    layer rounds it (swr.py:216)."""
+    B, L, H = a_logits.shape
+    a = torch.sigmoid(a_logits.float()).bfloat16().float().transpose(1, 2)
+    heads = lambda t: t.float().reshape(B, L, H, 16).permute(0, 2, 3, 1)
+    x = torch.sigmoid(heads(b_logits)) * heads(v)
+    y = O.btp_forward(a.contiguous(), x.contiguous(), k)
+    out = y * heads(c) + heads(v)
+    return out.permute(0, 3, 1, 2).reshape(B, L, H * 16)
+
+
+@pytest.mark.parametrize("B,L,H,sliced", [(2, 64, 4, False), (3, 208, 8, False), (2, 1024, 4, True), (40, 128, 16, False)])
+def test_gated_forward_vs_oracle(native, B, L, H, sliced):
+    from spear_b200.ops.btp.gated import gated_btp
+
+    g = torch.Generator().manual_seed(100 + L)
+    cols = H * 16
+    if sliced:  # the four inputs as column slices of one wide projection output
+        wide = torch.randn(B, L, 3 * cols + 8 * ((H + 7) // 8), generator=g).bfloat16().cuda()
+        bl, c, v = wide[..., :cols], wide[..., cols:2 * cols], wide[..., 2 * cols:3 * cols]
+        al = wide[..., 3 * cols:3 * cols + H]
+    else:
+        al = torch.randn(B, L, H, generator=g).bfloat16().cuda()
+        bl, c, v = (torch.randn(B, L, cols, generator=g).bfloat16().cuda() for _ in range(3))
+    for k in (2, 1):
+        out = gated_btp(al, bl, c, v, k)
+        want = _gated_oracle(al.cpu(), bl.cpu(), c.cpu(), v.cpu(), k)
+        assert out.shape == want.shape and torch.isfinite(out.float()).all()
+        m = O.error_metrics(out.float().cpu(), want)
+        assert m["rel_l2"] <= 1e-2, f"gated out k={k}: rel_l2 {m['rel_l2']:.3e}"
+
+
+def test_gated_backward_matches_unfused_layer(native):
+    """Fused layer vs the same layer run operation by operation: outputs and every gradient."""
+    from spear_b200.nn.phalanx import Phalanx
+
+    torch.manual_seed(3)
+    layer = Phalanx(dim=128, length=96, dtype=torch.bfloat16).cuda()
+    g = torch.Generator().manual_seed(4)
+    u = torch.randn(3, 96, 128, generator=g).cuda()
+    dout = torch.randn(3, 96, 128, generator=g).bfloat16().cuda()
+    res = {}
+    for fused in (True, False):
+        layer.fused_gating = fused
+        layer.zero_grad()
+        ui = u.clone().requires_grad_(True)
+        out = layer(ui)
+        out.backward(dout)
+        res[fused] = (out.detach().float().cpu(), ui.grad.float().cpu(), {n: p.grad.float().cpu() for n, p in layer.named_parameters()})
+    assert O.rel_l2(res[True][0], res[False][0]) <= 2e-2
+    assert O.rel_l2(res[True][1], res[False][1]) <= 3e-2
+    for name in res[True][2]:
+        assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 3e-2, name
