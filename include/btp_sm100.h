@@ -120,6 +120,20 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
                             int B, int L, int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
                             long long ld_out, int k, void* stream);
 
+/*
+ * Backward of btp_sm100_gated_forward, token-major throughout.  Replaces autograd through
+ * spear/nn/phalanx/swr.py:216-219 and 320-323, the transposing copies (interface.py:186-187, 154) and
+ * spear._btp.backward.  Everything the forward computed is recomputed from the four inputs.
+ *   dout                      [B, L, H*16] bf16  gradient of `out`
+ *   da_logits                 [B, L, H]    bf16  (pitch a multiple of 4 elements, base 8-byte aligned)
+ *   db_logits, dc, dv         [B, L, H*16] bf16
+ * Pitches (elements) follow the pointers in the same order; constraints as for the forward.
+ */
+int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
+                             void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H,
+                             long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_do,
+                             long long ld_da, long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream);
+
 /* Name of a status code ("BTP_OK", "BTP_ERR_BAD_SHAPE", ...).  Never NULL. */
 const char* btp_sm100_status_string(int status);
 

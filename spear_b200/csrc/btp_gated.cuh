@@ -52,10 +52,18 @@ __device__ __forceinline__ float logit_to_log2a(float z) {
   return (a > kTinyCoeff) ? lg2(a) : kZeroLog2;
 }
 
-// x = bf16(sigmoid(b) * v) for a pair of packed bf16 values
-__device__ __forceinline__ uint32_t gate_pair(uint32_t b, uint32_t v) {
-  return pack_bf16x2(sigmoid_fast(bf16_lo(b)) * bf16_lo(v), sigmoid_fast(bf16_hi(b)) * bf16_hi(v));
+// The layer's driving term for a pair of packed bf16 values, rounded where the layer rounds
+// (swr.py:217-219): sigma = bf16(sigmoid(b)), x = bf16(sigma * v).
+__device__ __forceinline__ uint32_t sigmoid_pair(uint32_t b) {
+  return pack_bf16x2(sigmoid_fast(bf16_lo(b)), sigmoid_fast(bf16_hi(b)));
 }
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t gate_pair(uint32_t b, uint32_t v) { return mul_bf16x2(sigmoid_pair(b), v); }
+__device__ __forceinline__ float gate_scalar(float b, float v) { return round_bf16(round_bf16(sigmoid_fast(b)) * v); }
 
 // carry of the 16-token block that starts at `tok0` of batch entry b, head h, recomputed from global memory
 __device__ __forceinline__ void gated_halo_left(const GatedParams& p, long long b, int h, int tok0, int lane,
@@ -76,9 +84,8 @@ __device__ __forceinline__ void gated_halo_left(const GatedParams& p, long long 
     const float w = round_bf16(ex2(T15 - __shfl_sync(0xffffffffu, T, tok)));
     const long long rb = (row0 + tok) * p.ld_b + h * 16;
     const long long rv = (row0 + tok) * p.ld_v + h * 16;
-    const float x_g = round_bf16(sigmoid_fast(__bfloat162float(p.b_logits[rb + g])) * __bfloat162float(p.v[rv + g]));
-    const float x_g8 =
-        round_bf16(sigmoid_fast(__bfloat162float(p.b_logits[rb + g + 8])) * __bfloat162float(p.v[rv + g + 8]));
+    const float x_g = gate_scalar(__bfloat162float(p.b_logits[rb + g]), __bfloat162float(p.v[rv + g]));
+    const float x_g8 = gate_scalar(__bfloat162float(p.b_logits[rb + g + 8]), __bfloat162float(p.v[rv + g + 8]));
     sg = fmaf(x_g, w, sg);
     sg8 = fmaf(x_g8, w, sg8);
   }

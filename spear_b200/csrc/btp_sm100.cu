@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "btp_gated.cuh"
+#include "btp_gated_bwd.cuh"
 #include "btp_kernels.cuh"
 
 namespace {
@@ -70,13 +71,13 @@ int make_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L
   return BTP_OK;
 }
 
-// Token-major tensor [B][L][cols] bf16 with row pitch `ld` elements; box = 64 tokens x 64 channels.
-int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, long long ld) {
+// Token-major tensor [B][L][cols] bf16 with row pitch `ld` elements; box = `box_rows` tokens x 64 channels.
+int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, long long ld, int box_rows = 64) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(ld) * 2 * L};
-  const cuuint32_t box[3] = {64u, 64u, 1u};
+  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -482,6 +483,68 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
   p.use_carry = (k == 2);
   p.interleave = (ncs <= 8) && (static_cast<long long>(B) * hgs >= 4ll * grid);
   kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_o, p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+
+int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
+                             void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, long long ld_a,
+                             long long ld_b, long long ld_c, long long ld_v, long long ld_do, long long ld_da,
+                             long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream) {
+  const char* fn = "btp_sm100_gated_backward";
+  if (B <= 0 || H <= 0 || L <= 0) return fail(BTP_ERR_BAD_SHAPE, "%s: B, L, H must be positive (got %d, %d, %d)", fn, B, L, H);
+  if (L % 16 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: L must be a multiple of 16 (got %d)", fn, L);
+  if (H % 4 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: the number of heads must be a multiple of 4 (got %d)", fn, H);
+  if (k != 1 && k != 2) return fail(BTP_ERR_BAD_ORDER, "%s: k must be 1 or 2 (got %d)", fn, k);
+  if (!a_logits || !b_logits || !c || !v || !dout || !da_logits || !db_logits || !dc || !dv)
+    return fail(BTP_ERR_NULL_POINTER, "%s: no pointer may be NULL", fn);
+  const long long cols = static_cast<long long>(H) * 16;
+  if (ld_a < H || ld_da < H || ld_b < cols || ld_c < cols || ld_v < cols || ld_do < cols || ld_db < cols || ld_dc < cols ||
+      ld_dv < cols)
+    return fail(BTP_ERR_BAD_SHAPE, "%s: a row pitch is smaller than its row", fn);
+  if (ld_b % 8 || ld_c % 8 || ld_v % 8 || ld_do % 8 || ld_db % 8 || ld_dc % 8 || ld_dv % 8 || ld_da % 4)
+    return fail(BTP_ERR_MISALIGNED, "%s: row pitches must be multiples of 8 elements (dA_logits: 4)", fn);
+  if (misaligned(b_logits) || misaligned(c) || misaligned(v) || misaligned(dout) || misaligned(db_logits) || misaligned(dc) ||
+      misaligned(dv) || (reinterpret_cast<uintptr_t>(a_logits) & 1u) || (reinterpret_cast<uintptr_t>(da_logits) & 7u))
+    return fail(BTP_ERR_MISALIGNED, "%s: the [B,L,H*16] tensors must be 16-byte aligned, dA_logits 8-byte aligned", fn);
+  const int hgs = H / 4;
+  const int ncs = (L + kGbTL - 1) / kGbTL;
+  const long long total = static_cast<long long>(B) * hgs * ncs;
+  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
+  constexpr int STAGES = 3;
+  using SM = GatedBwdSmem<STAGES>;
+  auto kern = btp_gated_backward_kernel<STAGES>;
+  static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = LN.prepare(dev, &ctas))) return rc;
+  CUtensorMap tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv;
+  const int icols = static_cast<int>(cols);
+  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, icols, ld_b, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_c, c, B, L, icols, ld_c, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_v, v, B, L, icols, ld_v, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_do, dout, B, L, icols, ld_do, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_db, db_logits, B, L, icols, ld_db, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_dc, dc, B, L, icols, ld_dc, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_dv, dv, B, L, icols, ld_dv, kGbTL))) return rc;
+  const long long cap = static_cast<long long>(info.sms) * ctas;
+  const int grid = static_cast<int>(total < cap ? total : cap);
+  GatedBwdParams p{};
+  p.a_logits = static_cast<const __nv_bfloat16*>(a_logits);
+  p.b_logits = static_cast<const __nv_bfloat16*>(b_logits);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.dout = static_cast<const __nv_bfloat16*>(dout);
+  p.da_logits = static_cast<__nv_bfloat16*>(da_logits);
+  p.ld_a = ld_a; p.ld_b = ld_b; p.ld_c = ld_c; p.ld_v = ld_v; p.ld_do = ld_do; p.ld_da = ld_da;
+  p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
+  p.use_carry = (k == 2);
+  p.interleave = (ncs <= 8) && (static_cast<long long>(B) * hgs >= 4ll * grid);
+  kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;

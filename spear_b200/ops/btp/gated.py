@@ -71,26 +71,51 @@ class _GatedBTP(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        # Unfused for now: the op's own backward kernel between elementwise CUDA passes.
         a_logits, b_logits, c, v = ctx.saved_tensors
-        B, L, H = a_logits.shape
-        a = torch.sigmoid(a_logits).transpose(1, 2).contiguous()
-        sb = torch.sigmoid(b_logits)
-        x = _to_heads(sb * v, H)
-        y = torch.empty_like(x)
-        _native.forward(a, x, y, None, ctx.k, 32)
-        dout = dout.contiguous()
-        dy = _to_heads(dout * c, H)
-        dx = torch.empty_like(x)
-        dA = torch.empty(a.shape, device=a.device, dtype=torch.float32)
-        _native.backward(a, x, dy, None, dx, dA, ctx.k, 32)
-        dx_t = _to_tokens(dx)
-        dc = dout * _to_tokens(y)
-        dv = dout + dx_t * sb
-        db = dx_t * v * (sb * (1 - sb))
-        af = a.float()
-        da_logits = (dA * af * (1 - af)).transpose(1, 2).to(a_logits.dtype)
-        return da_logits, db, dc, dv, None
+        if _FUSED_BACKWARD:
+            return _backward_fused(a_logits, b_logits, c, v, dout, ctx.k) + (None,)
+        return _backward_unfused(a_logits, b_logits, c, v, dout, ctx.k) + (None,)
+
+
+_FUSED_BACKWARD = True  # False: the op's own backward kernel between elementwise CUDA passes (for comparison)
+
+
+def _backward_fused(a_logits, b_logits, c, v, dout, k):
+    B, L, H = a_logits.shape
+    cols = H * 16
+    dout = dout if dout.stride(2) == 1 else dout.contiguous()
+    da = torch.empty(B, L, H, device=v.device, dtype=v.dtype)
+    db, dc, dv = (torch.empty(B, L, cols, device=v.device, dtype=v.dtype) for _ in range(3))
+    ld = [_rows(a_logits, H, "a_logits")] + [_rows(t, cols, n) for t, n in
+                                             ((b_logits, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"))]
+    ld += [H, cols, cols, cols]
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    with _native._OnDevice(v.device.index) as stream:
+        rc = _lib.load().btp_sm100_gated_backward(p(a_logits), p(b_logits), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
+                                                  B, L, H, *ld, int(k), ctypes.c_void_p(stream))
+    _lib.check(rc, "btp_sm100_gated_backward")
+    return da, db, dc, dv
+
+
+def _backward_unfused(a_logits, b_logits, c, v, dout, k):
+    B, L, H = a_logits.shape
+    a = torch.sigmoid(a_logits).transpose(1, 2).contiguous()
+    sb = torch.sigmoid(b_logits)
+    x = _to_heads(sb * v, H)
+    y = torch.empty_like(x)
+    _native.forward(a, x, y, None, k, 32)
+    dout = dout.contiguous()
+    dy = _to_heads(dout * c, H)
+    dx = torch.empty_like(x)
+    dA = torch.empty(a.shape, device=a.device, dtype=torch.float32)
+    _native.backward(a, x, dy, None, dx, dA, k, 32)
+    dx_t = _to_tokens(dx)
+    dc = dout * _to_tokens(y)
+    dv = dout + dx_t * sb
+    db = dx_t * v * (sb * (1 - sb))
+    af = a.float()
+    da_logits = (dA * af * (1 - af)).transpose(1, 2).to(a_logits.dtype)
+    return da_logits, db, dc, dv
 
 
 def gated_btp(a_logits: torch.Tensor, b_logits: torch.Tensor, c: torch.Tensor, v: torch.Tensor, k: int = 2) -> torch.Tensor:
