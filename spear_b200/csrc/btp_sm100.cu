@@ -203,14 +203,14 @@ int set_chunks(const char* fn, Dims* d, int TL) {
   return BTP_OK;
 }
 
-// Whole sequences are dealt round-robin to the warps when they are short (at most 8 chunks) and numerous
-// enough (at least 4 per warp) for that to balance; otherwise every warp takes a contiguous range of chunks.
+// Whole sequences are dealt round-robin to the warps when they are numerous enough (at least 4 per warp) for
+// that to balance; otherwise every warp takes a contiguous range of chunks.
 bool use_interleave(const Dims& d, long long nwarps) {
   static const bool enabled = [] {
     const char* e = getenv("BTP_SM100_INTERLEAVE");
     return e ? atoi(e) != 0 : true;
   }();
-  return enabled && d.ncs <= 8 && d.BH >= 4 * nwarps;
+  return enabled && d.BH >= 4 * nwarps;
 }
 
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
@@ -481,7 +481,7 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
   p.ld_a = ld_a; p.ld_b = ld_b; p.ld_v = ld_v;
   p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
   p.use_carry = (k == 2);
-  p.interleave = (ncs <= 8) && (static_cast<long long>(B) * hgs >= 4ll * grid);
+  p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
   kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_o, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -543,7 +543,7 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
   p.ld_a = ld_a; p.ld_b = ld_b; p.ld_c = ld_c; p.ld_v = ld_v; p.ld_do = ld_do; p.ld_da = ld_da;
   p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
   p.use_carry = (k == 2);
-  p.interleave = (ncs <= 8) && (static_cast<long long>(B) * hgs >= 4ll * grid);
+  p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
   kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
