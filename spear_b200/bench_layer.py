@@ -1,0 +1,109 @@
+"""Timing of the gated (token-major) op and of the whole Phalanx layer on one GPU.
+
+    python -m spear_b200.bench_layer [--batch 1024 --length 128 --dim 512] [--steps 50] [--what gated|layer|both]
+
+`gated`: one fused forward + one fused backward launch per step on resident inputs; reports time per
+launch and achieved GB/s against the algorithmic bytes (forward 130 B, backward 228 B per head-token:
+inputs read once, outputs written once).  `layer`: Phalanx forward+backward through autograd, with the
+gating fused and, for comparison, operation by operation.  Synthetic N(0,1) inputs, CUDA events, rotating
+input sets so that successive launches do not find their inputs in L2.  One JSON line per measurement.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+GATED_FWD_BYTES = 130  # per head-token: A 2 + B 32 + C 32 + V 32 read, out 32 written
+GATED_BWD_BYTES = 228  # A 2 + B, C, V, dOut 128 read; dA 2 + dB, dC, dV 96 written
+
+
+def _timed(fn, steps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps * 1e3  # us
+
+
+def bench_gated(B, L, H, steps, sets):
+    from spear_b200 import _lib
+    from spear_b200.ops.btp import gated as G
+
+    cols = H * 16
+    data = []
+    for _ in range(sets):
+        al = torch.randn(B, L, H, device="cuda").bfloat16()
+        bl, c, v, do = (torch.randn(B, L, cols, device="cuda").bfloat16() for _ in range(4))
+        data.append((al, bl, c, v, do, torch.empty_like(v)))
+    i = [0]
+
+    def fwd():
+        al, bl, c, v, do, out = data[i[0] % sets]
+        i[0] += 1
+        G._forward_impl(al, bl, c, v, out, 2)
+
+    def bwd():
+        al, bl, c, v, do, out = data[i[0] % sets]
+        i[0] += 1
+        G._backward_fused(al, bl, c, v, do, 2)
+
+    ht = B * L * H
+    tf, tb = _timed(fwd, steps), _timed(bwd, steps)
+    _lib.device_status()
+    return {
+        "what": "gated_btp", "B": B, "L": L, "H": H, "fwd_us": tf, "bwd_us": tb,
+        "fwd_gbs": GATED_FWD_BYTES * ht / tf / 1e3, "bwd_gbs": GATED_BWD_BYTES * ht / tb / 1e3,
+        "fwd_bwd_tokens_per_s": B * L / ((tf + tb) * 1e-6),
+    }
+
+
+def bench_layer(B, L, dim, steps):
+    from spear_b200.nn.phalanx import Phalanx
+
+    torch.manual_seed(0)
+    layer = Phalanx(dim=dim, length=L, dtype=torch.bfloat16).cuda()
+    u = torch.randn(B, L, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    do = torch.randn(B, L, dim, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        layer.zero_grad(set_to_none=True)
+        u.grad = None
+        layer(u).backward(do)
+
+    out = {"what": "phalanx_layer_fwd_bwd", "B": B, "L": L, "dim": dim}
+    for fused in (True, False):
+        layer.fused_gating = fused
+        t = _timed(step, steps, warm=2)
+        out["fused_ms" if fused else "unfused_ms"] = t / 1e3
+    out["tokens_per_s_fused"] = B * L / (out["fused_ms"] * 1e-3)
+    out["speedup"] = out["unfused_ms"] / out["fused_ms"]
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1024)
+    ap.add_argument("--length", type=int, default=128)
+    ap.add_argument("--dim", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--sets", type=int, default=3)
+    ap.add_argument("--what", default="both", choices=["gated", "layer", "both"])
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device")
+    if args.what in ("gated", "both"):
+        print(json.dumps(bench_gated(args.batch, args.length, args.dim // 16, args.steps, args.sets)), flush=True)
+    if args.what in ("layer", "both"):
+        print(json.dumps(bench_layer(args.batch, args.length, args.dim, max(3, args.steps // 10))), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,7 +33,7 @@ def test_every_declared_symbol_is_exported(lib):
     from spear_b200 import _lib
 
     names = declared_functions()
-    assert len(names) >= 8
+    assert len(names) >= 10
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/btp_sm100.h but not exported"
     assert sorted(_lib.SYMBOLS) == names, "the ctypes prototypes and the header disagree"
@@ -81,6 +81,30 @@ def test_argument_errors_come_back_as_codes(lib):
     assert _bwd(lib, dd=2) == -4
     assert _bwd(lib, dA=0) == -1
     assert _bwd(lib, dx=24) == -5
+
+
+def test_gated_entry_points_check_their_arguments(lib):
+    p, ll = ctypes.c_void_p, ctypes.c_longlong
+
+    def fwd(B=1, L=16, H=4, k=2, ld=(4, 64, 64, 64, 64), ptrs=(16, 16, 16, 16, 16)):
+        return lib.btp_sm100_gated_forward(*[p(x) for x in ptrs], B, L, H, *[ll(x) for x in ld], k, p(0))
+
+    def bwd(B=1, L=16, H=4, k=2, ld=(4, 64, 64, 64, 64, 4, 64, 64, 64), ptrs=(16,) * 9):
+        return lib.btp_sm100_gated_backward(*[p(x) for x in ptrs], B, L, H, *[ll(x) for x in ld], k, p(0))
+
+    assert fwd(H=6) == -2 and "multiple of 4" in lib.btp_sm100_last_error().decode()
+    assert fwd(L=24) == -2
+    assert fwd(k=0) == -3
+    assert fwd(ptrs=(16, 0, 16, 16, 16)) == -1
+    assert fwd(ld=(4, 60, 64, 64, 64)) == -2      # pitch smaller than the row
+    assert fwd(ld=(4, 68, 64, 64, 64)) == -5      # pitch not a multiple of 8 elements
+    assert fwd(ptrs=(16, 8, 16, 16, 16)) == -5
+    assert bwd(H=2) == -2
+    assert bwd(L=8) == -2
+    assert bwd(k=3) == -3
+    assert bwd(ptrs=(16,) * 8 + (0,)) == -1
+    assert bwd(ld=(4, 64, 64, 64, 64, 6, 64, 64, 64)) == -5
+    assert bwd(ptrs=(16, 16, 16, 16, 16, 4, 16, 16, 16)) == -5
 
 
 def test_no_gpu_is_an_error_not_a_fallback(lib):
