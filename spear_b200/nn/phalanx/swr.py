@@ -160,13 +160,21 @@ class Phalanx(nn.Module):
         # The gating around the op runs fused, in the projections' own token-major layout, whenever the kernel
         # supports the configuration; set to False for the reference's operation-by-operation data flow.
         self.fused_gating = True
+        # With fused gating and heads % 8 == 0 the four projections (swr.py:157-175) run as ONE GEMM whose
+        # output columns (b | c | v | a) the gated kernel reads in place; the parameters stay separate.
+        self.fused_projection = True
 
     def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
-        from spear_b200.ops.btp.gated import gated_btp
+        from spear_b200.ops.btp.gated import gated_btp, gated_btp_wide
 
         u = x.to(self.compute_dtype)
         prm = self.param
-        y = gated_btp(prm.proj_a(u), prm.proj_b(u), prm.proj_c(u), prm.proj_v(u), self.k)
+        if self.fused_projection and self.heads % 8 == 0:
+            weight = torch.cat([prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight], dim=0)
+            bias = torch.cat([prm.proj_b.bias, prm.proj_c.bias, torch.zeros_like(prm.proj_b.bias), prm.proj_a.bias])
+            y = gated_btp_wide(nn.functional.linear(u, weight, bias), self.heads, self.k)
+        else:
+            y = gated_btp(prm.proj_a(u), prm.proj_b(u), prm.proj_c(u), prm.proj_v(u), self.k)
         return self.proj_out(y)
 
     def _forward_default(self, x: torch.Tensor) -> torch.Tensor:

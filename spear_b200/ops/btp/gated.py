@@ -16,7 +16,7 @@ import torch
 from ... import _btp as _native
 from ... import _lib
 
-__all__ = ["gated_btp", "gated_btp_supported"]
+__all__ = ["gated_btp", "gated_btp_wide", "gated_btp_supported"]
 
 
 def gated_btp_supported(heads: int, kv_heads: int, length: int) -> bool:
@@ -116,6 +116,57 @@ def _backward_unfused(a_logits, b_logits, c, v, dout, k):
     af = a.float()
     da_logits = (dA * af * (1 - af)).transpose(1, 2).to(a_logits.dtype)
     return da_logits, db, dc, dv
+
+
+def _split_wide(wide: torch.Tensor, H: int):
+    """Column slices (b_logits, c, v, a_logits) of a [B, L, 3*H*16 + H] projection output."""
+    d = H * 16
+    return wide[..., :d], wide[..., d:2 * d], wide[..., 2 * d:3 * d], wide[..., 3 * d:3 * d + H]
+
+
+class _GatedBTPWide(torch.autograd.Function):
+    """Same op on the output of ONE wide projection; the backward kernel writes the four gradients straight
+    into the column slices of one gradient tensor, so nothing is concatenated or zero-filled."""
+
+    @staticmethod
+    def forward(ctx, wide, heads, k):
+        bl, c, v, al = _split_wide(wide, heads)
+        out = torch.empty(v.shape, device=v.device, dtype=v.dtype)
+        _forward_impl(al, bl, c, v, out, k)
+        ctx.save_for_backward(wide)
+        ctx.heads, ctx.k = int(heads), int(k)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (wide,) = ctx.saved_tensors
+        H, k = ctx.heads, ctx.k
+        bl, c, v, al = _split_wide(wide, H)
+        dwide = torch.empty_like(wide)
+        db, dc, dv, da = _split_wide(dwide, H)
+        dout = dout if dout.stride(2) == 1 else dout.contiguous()
+        B, L, _ = al.shape
+        cols = H * 16
+        ld = [_rows(al, H, "a_logits")] + [_rows(t, cols, n) for t, n in ((bl, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"))]
+        ld += [_rows(da, H, "da_logits")] + [_rows(t, cols, n) for t, n in ((db, "db"), (dc, "dc"), (dv, "dv"))]
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        with _native._OnDevice(v.device.index) as stream:
+            rc = _lib.load().btp_sm100_gated_backward(p(al), p(bl), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
+                                                      B, L, H, *ld, k, ctypes.c_void_p(stream))
+        _lib.check(rc, "btp_sm100_gated_backward")
+        return dwide, None, None
+
+
+def gated_btp_wide(wide: torch.Tensor, heads: int, k: int = 2) -> torch.Tensor:
+    """gated_btp on one projection output `wide` [B, L, 3*heads*16 + heads] whose columns are
+    (b_logits | c | v | a_logits).  heads must be a multiple of 8 (16-byte aligned column slices)."""
+    if wide.dim() != 3 or wide.shape[2] != 3 * heads * 16 + heads:
+        raise ValueError(f"wide must be [B, L, {3 * heads * 16 + heads}], got {tuple(wide.shape)}")
+    if heads % 8 != 0 or wide.shape[1] % 16 != 0:
+        raise ValueError("gated_btp_wide needs heads % 8 == 0 and L % 16 == 0")
+    if not wide.is_contiguous():
+        wide = wide.contiguous()
+    return _GatedBTPWide.apply(wide, heads, k)
 
 
 def gated_btp(a_logits: torch.Tensor, b_logits: torch.Tensor, c: torch.Tensor, v: torch.Tensor, k: int = 2) -> torch.Tensor:

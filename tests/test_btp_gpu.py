@@ -434,3 +434,26 @@ def test_gated_backward_vs_oracle(native, B, L, H):
             assert torch.isfinite(got.grad.float()).all(), name
             err = O.rel_l2(got.grad.float().cpu(), exp.grad)
             assert err <= 1.5e-2, f"{name} k={k}: rel_l2 {err:.3e}"
+
+
+def test_fused_projection_matches_separate_projections(native):
+    """One wide GEMM feeding the gated kernels through row pitches vs four projections: same layer results."""
+    from spear_b200.nn.phalanx import Phalanx
+
+    torch.manual_seed(5)
+    layer = Phalanx(dim=128, length=80, dtype=torch.bfloat16).cuda()  # 8 heads
+    g = torch.Generator().manual_seed(6)
+    u = torch.randn(2, 80, 128, generator=g).cuda()
+    dout = torch.randn(2, 80, 128, generator=g).bfloat16().cuda()
+    res = {}
+    for wide in (True, False):
+        layer.fused_projection = wide
+        layer.zero_grad()
+        ui = u.clone().requires_grad_(True)
+        out = layer(ui)
+        out.backward(dout)
+        res[wide] = (out.detach().float().cpu(), ui.grad.float().cpu(), {n: p.grad.float().cpu() for n, p in layer.named_parameters()})
+    assert O.rel_l2(res[True][0], res[False][0]) <= 1e-2
+    assert O.rel_l2(res[True][1], res[False][1]) <= 2e-2
+    for name in res[True][2]:
+        assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
