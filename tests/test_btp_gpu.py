@@ -457,3 +457,30 @@ def test_fused_projection_matches_separate_projections(native):
     assert O.rel_l2(res[True][1], res[False][1]) <= 2e-2
     for name in res[True][2]:
         assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
+
+
+def test_forward_backward_replay_from_a_cuda_graph(native):
+    """The calls only enqueue work on the given stream (descriptors travel by value), so a captured
+    forward+backward replays on new data in the same buffers."""
+    a, x, dy = sample(4, 8, 256, 31)
+    ad, xd, dyd = dev(a, torch.bfloat16), dev(x, torch.bfloat16), dev(dy, torch.bfloat16)
+    y, dx = torch.empty_like(xd), torch.empty_like(xd)
+    dA = torch.empty(4, 8, 256, device="cuda")
+    native.forward(ad, xd, y, None, 2, 32)   # first calls set the kernels' attributes: keep them out of the capture
+    native.backward(ad, xd, dyd, None, dx, dA, 2, 32)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            native.forward(ad, xd, y, None, 2, 32)
+            native.backward(ad, xd, dyd, None, dx, dA, 2, 32)
+    a2, x2, dy2 = sample(4, 8, 256, 32)
+    ad.copy_(dev(a2, torch.bfloat16)); xd.copy_(dev(x2, torch.bfloat16)); dyd.copy_(dev(dy2, torch.bfloat16))
+    y.zero_(); dx.zero_(); dA.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert_limits(y.float().cpu(), O.btp_forward(a2, x2), FORWARD_LIMITS, "y from graph")
+    dA_w, dx_w = O.btp_backward(a2, x2, dy2)
+    assert_limits(dx.float().cpu(), dx_w, BACKWARD_LIMITS, "dx from graph")
+    assert_limits(dA.cpu(), dA_w, BACKWARD_LIMITS, "dA from graph")
