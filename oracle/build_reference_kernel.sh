@@ -6,9 +6,9 @@
 # repository; oracle/_ref/ is git-ignored.  Needs: nvcc, torch headers, CUTLASS headers (the image ships
 # them inside the flashinfer wheel).  One translation unit, about four minutes.
 #
-#   oracle/build_reference_kernel.sh [/path/to/reference]
+#   oracle/build_reference_kernel.sh /path/to/reference      (or set SPEAR_REFERENCE)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${SPEAR_REFERENCE:?give the path of the reference checkout}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 mkdir -p "$OUT"

@@ -5,7 +5,7 @@ the float32/float64 oracle.  Test infrastructure, not a product path.
 Only shapes whose sequences fit one CTA of the reference kernel (L/16 <= wpb) are run: there its cluster has
 one CTA and none of its unbounded cluster-barrier waits is ever entered (csrc/btp/btp-forward.cu:340-347).
 
-    python oracle/compare_reference_kernel.py [--out gpurun_out/reference_kernel.json]
+    python oracle/compare_reference_kernel.py [--out reference_kernel.json]
 """
 
 from __future__ import annotations
