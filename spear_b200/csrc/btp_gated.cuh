@@ -36,13 +36,12 @@ struct GatedParams {
   int interleave;                 // deal whole sequences round-robin to the CTAs
 };
 
-constexpr int kGatedTL = 64;        // tokens per chunk
-constexpr int kGatedBox = 64 * 128;  // bytes of one [64 tokens][64 channels] bf16 box
-
-template <int STAGES>
+// TL = tokens per chunk (32 or 64): one box is [TL tokens][64 channels] bf16.
+template <int TL, int STAGES>
 struct GatedSmem {
-  static constexpr int kStage = 3 * kGatedBox;           // B_logits, C, V
-  static constexpr int kTables = 4 * 2 * kGatedTL * 4;   // per warp: T, P
+  static constexpr int kBox = TL * 128;
+  static constexpr int kStage = 3 * kBox;           // B_logits, C, V
+  static constexpr int kTables = 4 * 2 * TL * 4;    // per warp: T, P
   static constexpr int kBytes = STAGES * kStage + kTables + STAGES * 8;
 };
 
@@ -116,14 +115,16 @@ struct GatedCursor {
   }
 };
 
-template <int STAGES>
+template <int TL, int STAGES>
 __global__ void __launch_bounds__(128)
 btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_out,
                          const GatedParams p) {
   static_assert(STAGES >= 3, "compute, draining store and load in flight need three stages");
-  constexpr int TL = kGatedTL;
-  using SM = GatedSmem<STAGES>;
+  constexpr int TPL = TL / 32;  // tokens (logits) per lane and chunk
+  constexpr int NT = TL / 16;   // blocks per chunk
+  using SM = GatedSmem<TL, STAGES>;
+  constexpr int kGatedBox = SM::kBox;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -170,19 +171,19 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
     s_prod = (s_prod + 1 == STAGES) ? 0 : s_prod + 1;
   };
   // the two logits this lane owns in a chunk (tokens 2*lane, 2*lane+1 of the warp's head)
-  auto load_logits = [&](const GatedCursor& c, float& z0, float& z1) {
-    const int tok = c.cs * TL + 2 * lane;
+  auto load_logits = [&](const GatedCursor& c, float (&z)[TPL]) {
+    const int tok = c.cs * TL + TPL * lane;
     const long long row = static_cast<long long>(c.b) * L + tok;
     const int h = c.hg * 4 + warp;
-    z0 = (tok < L) ? __bfloat162float(p.a_logits[row * p.ld_a + h]) : 0.0f;
-    z1 = (tok + 1 < L) ? __bfloat162float(p.a_logits[(row + 1) * p.ld_a + h]) : 0.0f;
+#pragma unroll
+    for (int q = 0; q < TPL; ++q) z[q] = (tok + q < L) ? __bfloat162float(p.a_logits[(row + q) * p.ld_a + h]) : 0.0f;
   };
 
   constexpr int AHEAD = STAGES - 2;
   for (int k = 0; k < AHEAD && k < n; ++k) issue();
   GatedCursor peek = cons;  // runs one unit ahead of the consumer for the logit prefetch
-  float zn0, zn1;
-  load_logits(peek, zn0, zn1);
+  float zn[TPL];
+  load_logits(peek, zn);
   peek.next(ncs, hgs);
 
   // lane-constant addressing of this warp's [16 tokens][16 channels] block inside a box (see the header)
@@ -197,9 +198,11 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
       if (tid == 0) bulk_wait_group_read<1>();
       issue();
     }
-    const float z0 = zn0, z1 = zn1;
+    float l2[TPL];
+#pragma unroll
+    for (int q = 0; q < TPL; ++q) l2[q] = logit_to_log2a(zn[q]);
     if (j + 1 < n) {
-      load_logits(peek, zn0, zn1);
+      load_logits(peek, zn);
       peek.next(ncs, hgs);
     }
     const bool ok = mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);
@@ -209,8 +212,7 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
     }
     const int c0 = cons.cs * TL;
     const int left = (L - c0) >> 4;
-    const int nt = left < 4 ? left : 4;
-    const float l2[2] = {logit_to_log2a(z0), logit_to_log2a(z1)};
+    const int nt = left < NT ? left : NT;
     tables_from_log2<TL, false>(l2, tab, lane, carry_scale);
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
@@ -223,7 +225,7 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
     const uint32_t sc = sb + kGatedBox;
     const uint32_t sv = sb + 2 * kGatedBox;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < NT; ++i) {
       if (i < nt) {
         uint32_t bf[4], vf[4], cf[4];
         ldmatrix_x4_trans(sb + 2048 * i, bf[0], bf[1], bf[2], bf[3]);

@@ -189,8 +189,8 @@ __device__ __forceinline__ int chunk_tiles(int cs, int L) {
 // term off without a single extra instruction per block.
 template <int TL, bool BWD>
 __device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], float* tab, int lane, float carry_scale) {
-  constexpr int TPL = TL / 32;    // tokens per lane: 2 or 4
-  constexpr int LPT = 16 / TPL;   // lanes per block: 8 or 4
+  constexpr int TPL = TL / 32;    // tokens per lane: 1, 2 or 4
+  constexpr int LPT = 16 / TPL;   // lanes per block: 16, 8 or 4
   float T[TPL];
   T[0] = l2[0];
 #pragma unroll
@@ -233,10 +233,14 @@ __device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], flo
     reinterpret_cast<float4*>(tab)[lane] = make_float4(T[0], T[1], T[2], T[3]);
     reinterpret_cast<float4*>(tab + TL)[lane] = make_float4(second[0], second[1], second[2], second[3]);
     if constexpr (BWD) reinterpret_cast<float4*>(tab + 2 * TL)[lane] = make_float4(third[0], third[1], third[2], third[3]);
-  } else {
+  } else if constexpr (TPL == 2) {
     reinterpret_cast<float2*>(tab)[lane] = make_float2(T[0], T[1]);
     reinterpret_cast<float2*>(tab + TL)[lane] = make_float2(second[0], second[1]);
     if constexpr (BWD) reinterpret_cast<float2*>(tab + 2 * TL)[lane] = make_float2(third[0], third[1]);
+  } else {
+    tab[lane] = T[0];
+    tab[TL + lane] = second[0];
+    if constexpr (BWD) tab[2 * TL + lane] = third[0];
   }
   __syncwarp();
 }

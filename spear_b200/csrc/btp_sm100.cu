@@ -339,6 +339,55 @@ int backward_variant(const void* coeff, const void* x, const void* dy, void* dx,
   return launch_backward<COEF, DY_F32, 1, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
 }
 
+// ------------------------------------------------------------------ gated forward launch
+int gated_forward_variant() {
+  static const int v = [] {
+    const char* e = getenv("BTP_SM100_GATED_VARIANT");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
+template <int TL, int STAGES>
+int launch_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out, int B, int L,
+                         int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_out, int k,
+                         void* stream) {
+  const char* fn = "btp_sm100_gated_forward";
+  const long long cols = static_cast<long long>(H) * 16;
+  const int hgs = H / 4;
+  const int ncs = (L + TL - 1) / TL;
+  const long long total = static_cast<long long>(B) * hgs * ncs;
+  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
+  using SM = GatedSmem<TL, STAGES>;
+  auto kern = btp_gated_forward_kernel<TL, STAGES>;
+  static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = LN.prepare(dev, &ctas))) return rc;
+  CUtensorMap tm_b, tm_c, tm_v, tm_o;
+  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, static_cast<int>(cols), ld_b, TL))) return rc;
+  if ((rc = make_map_tokens(&tm_c, c, B, L, static_cast<int>(cols), ld_c, TL))) return rc;
+  if ((rc = make_map_tokens(&tm_v, v, B, L, static_cast<int>(cols), ld_v, TL))) return rc;
+  if ((rc = make_map_tokens(&tm_o, out, B, L, static_cast<int>(cols), ld_out, TL))) return rc;
+  const long long cap = static_cast<long long>(info.sms) * ctas;
+  const int grid = static_cast<int>(total < cap ? total : cap);
+  GatedParams p{};
+  p.a_logits = static_cast<const __nv_bfloat16*>(a_logits);
+  p.b_logits = static_cast<const __nv_bfloat16*>(b_logits);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.ld_a = ld_a; p.ld_b = ld_b; p.ld_v = ld_v;
+  p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
+  p.use_carry = (k == 2);
+  p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
+  kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_o, p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+
 // ------------------------------------------------------------------ built-in scratch for btp_sm100_forward_noalloc
 // Lives in the library image: every GPU that loads the library holds these 4 MiB until the process exits.
 // `g_noalloc_ckpt` is only a host-side handle in host code; kernels get the device address that
@@ -453,39 +502,11 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
     return fail(BTP_ERR_MISALIGNED, "%s: row pitches of B_logits, C, V and out must be multiples of 8 elements", fn);
   if (misaligned(b_logits) || misaligned(c) || misaligned(v) || misaligned(out) || (reinterpret_cast<uintptr_t>(a_logits) & 1u))
     return fail(BTP_ERR_MISALIGNED, "%s: B_logits, C, V and out must be 16-byte aligned", fn);
-  const int hgs = H / 4;
-  const int ncs = (L + kGatedTL - 1) / kGatedTL;
-  const long long total = static_cast<long long>(B) * hgs * ncs;
-  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
-  constexpr int STAGES = 3;
-  using SM = GatedSmem<STAGES>;
-  auto kern = btp_gated_forward_kernel<STAGES>;
-  static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
-  int dev;
-  DeviceInfo info;
-  int rc = device_info(&dev, &info);
-  if (rc) return rc;
-  int ctas;
-  if ((rc = LN.prepare(dev, &ctas))) return rc;
-  CUtensorMap tm_b, tm_c, tm_v, tm_o;
-  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, static_cast<int>(cols), ld_b))) return rc;
-  if ((rc = make_map_tokens(&tm_c, c, B, L, static_cast<int>(cols), ld_c))) return rc;
-  if ((rc = make_map_tokens(&tm_v, v, B, L, static_cast<int>(cols), ld_v))) return rc;
-  if ((rc = make_map_tokens(&tm_o, out, B, L, static_cast<int>(cols), ld_out))) return rc;
-  const long long cap = static_cast<long long>(info.sms) * ctas;
-  const int grid = static_cast<int>(total < cap ? total : cap);
-  GatedParams p{};
-  p.a_logits = static_cast<const __nv_bfloat16*>(a_logits);
-  p.b_logits = static_cast<const __nv_bfloat16*>(b_logits);
-  p.v = static_cast<const __nv_bfloat16*>(v);
-  p.ld_a = ld_a; p.ld_b = ld_b; p.ld_v = ld_v;
-  p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
-  p.use_carry = (k == 2);
-  p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
-  kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_o, p);
-  BTP_CUDA_TRY(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return BTP_OK;
+  const int variant_id = gated_forward_variant();
+  // measured on B200: 64-token chunks x 3 stages beat 32-token chunks with 3, 4 or 5 stages except at L = 128
+  if (variant_id == 1) return launch_gated_forward<32, 3>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
+  if (variant_id == 2) return launch_gated_forward<32, 4>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
+  return launch_gated_forward<64, 3>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
 }
 
 int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
