@@ -126,6 +126,36 @@ def make_layer_fixture(root: str):
         print(f"wrote {name}.npz")
 
 
+def make_inference_fixture(root: str):
+    """Outputs of the reference's prefill + decode helpers (spear/nn/phalanx/inference.py), float32 on CPU."""
+    sys.path.insert(0, root)
+    sys.modules.setdefault("spear._btp", types.ModuleType("spear._btp"))
+    from spear.nn.phalanx.inference import parallel_jagged, step_jagged  # noqa: WPS433
+
+    g = torch.Generator().manual_seed(4321)
+    data = {}
+    for L in (40, 64, 7):
+        B, H, D, steps = 2, 3, 16, 20
+        total = L + steps
+        A = _bf16_grid(torch.sigmoid(torch.randn(B, H, total, generator=g)))
+        X = _bf16_grid(torch.randn(B, H, D, total, generator=g))
+        C = _bf16_grid(torch.randn(B, H, D, total, generator=g))
+        V = _bf16_grid(torch.randn(B, H, D, total, generator=g))
+        Y, st = parallel_jagged(A[..., :L], X[..., :L], C[..., :L], V[..., :L], block_len=16)
+        ys = []
+        for t in range(L, total):
+            y_t, st = step_jagged(A[..., t], X[..., t], C[..., t], V[..., t], st)
+            ys.append(y_t)
+        pre = f"L{L}:"
+        data.update({pre + "A": A.numpy(), pre + "X": X.numpy(), pre + "C": C.numpy(), pre + "V": V.numpy(),
+                     pre + "Y": Y.numpy(), pre + "Ydec": torch.stack(ys, dim=-1).numpy()})
+        _, st0 = parallel_jagged(A[..., :L], X[..., :L], C[..., :L], V[..., :L], block_len=16)
+        data.update({pre + "h_loc": st0.h_loc.numpy(), pre + "r_pref": st0.r_pref.numpy(),
+                     pre + "c_prev_loc": st0.c_prev_loc.numpy(), pre + "i": np.array(st0.i)})
+    np.savez_compressed(os.path.join(HERE, "inference.npz"), **data)
+    print("wrote inference.npz")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -133,3 +163,4 @@ if __name__ == "__main__":
     torch.set_num_threads(4)
     make_op_fixtures(_load_reference_math(args.reference))
     make_layer_fixture(args.reference)
+    make_inference_fixture(args.reference)
