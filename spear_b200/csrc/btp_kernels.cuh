@@ -758,34 +758,37 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const float2 Sb = *reinterpret_cast<const float2*>(tt_i + TL + 8);      // P[2t+7], P[2t+8]
     const float2 La = *reinterpret_cast<const float2*>(tt_i + 2 * TL);      // Lmat[15, 2t], Lmat[15, 2t+1]
     const float2 Lb = *reinterpret_cast<const float2*>(tt_i + 2 * TL + 8);  // Lmat[15, 2t+8], Lmat[15, 2t+9]
-    float dx0[4], dx1[4];
-    dx0[0] = fmaf(La.x, dc_g, acc.g0[0]);  dx0[1] = fmaf(La.y, dc_g, acc.g0[1]);
-    dx0[2] = fmaf(La.x, dc_g8, acc.g0[2]); dx0[3] = fmaf(La.y, dc_g8, acc.g0[3]);
-    dx1[0] = fmaf(Lb.x, dc_g, acc.g1[0]);  dx1[1] = fmaf(Lb.y, dc_g, acc.g1[1]);
-    dx1[2] = fmaf(Lb.x, dc_g8, acc.g1[2]); dx1[3] = fmaf(Lb.y, dc_g8, acc.g1[3]);
+    // Packed fp32x2 arithmetic (one instruction for a token pair): the accumulator registers already hold
+    // tokens (2t, 2t+1) of a channel side by side.
+    const float2 dcg = make_float2(dc_g, dc_g), dcg8 = make_float2(dc_g8, dc_g8);
+    const float2 g0a = make_float2(acc.g0[0], acc.g0[1]), g0b = make_float2(acc.g0[2], acc.g0[3]);
+    const float2 g1a = make_float2(acc.g1[0], acc.g1[1]), g1b = make_float2(acc.g1[2], acc.g1[3]);
+    const float2 dxa = __ffma2_rn(La, dcg, g0a);   // channel g,   tokens 2t, 2t+1
+    const float2 dxb = __ffma2_rn(La, dcg8, g0b);  // channel g+8
+    const float2 dxc = __ffma2_rn(Lb, dcg, g1a);   // channel g,   tokens 8+2t, 9+2t
+    const float2 dxd = __ffma2_rn(Lb, dcg8, g1b);  // channel g+8
+    const float dx0[4] = {dxa.x, dxa.y, dxb.x, dxb.y};
+    const float dx1[4] = {dxc.x, dxc.y, dxd.x, dxd.y};
     // v shifted right by one token
     const int src = (lane & ~3) | ((lane + 3) & 3);
     const float A_g = __shfl_sync(0xffffffffu, acc.v0[1], src);
     const float A_g8 = __shfl_sync(0xffffffffu, acc.v0[3], src);
     const float B_g = __shfl_sync(0xffffffffu, acc.v1[1], src);
     const float B_g8 = __shfl_sync(0xffffffffu, acc.v1[3], src);
-    const float vp0_g = tl.t ? A_g : 0.0f, vp0_g8 = tl.t ? A_g8 : 0.0f;
-    const float vp2_g = tl.t ? B_g : A_g, vp2_g8 = tl.t ? B_g8 : A_g8;
-    float m0 = fmaf(vp0_g, dx0[0], vp0_g8 * dx0[2]);
-    float m1 = fmaf(acc.v0[0], dx0[1], acc.v0[2] * dx0[3]);
-    float m2 = fmaf(vp2_g, dx1[0], vp2_g8 * dx1[2]);
-    float m3 = fmaf(acc.v1[0], dx1[1], acc.v1[2] * dx1[3]);
-    m0 = fmaf(Sa.x, fmaf(acc.g0[0], cg, acc.g0[2] * cg8), m0);
-    m1 = fmaf(Sa.y, fmaf(acc.g0[1], cg, acc.g0[3] * cg8), m1);
-    m2 = fmaf(Sb.x, fmaf(acc.g1[0], cg, acc.g1[2] * cg8), m2);
-    m3 = fmaf(Sb.y, fmaf(acc.g1[1], cg, acc.g1[3] * cg8), m3);
+    const float2 vpa = make_float2(tl.t ? A_g : 0.0f, acc.v0[0]), vpb = make_float2(tl.t ? A_g8 : 0.0f, acc.v0[2]);
+    const float2 vpc = make_float2(tl.t ? B_g : A_g, acc.v1[0]), vpd = make_float2(tl.t ? B_g8 : A_g8, acc.v1[2]);
+    const float2 cg2 = make_float2(cg, cg), cg82 = make_float2(cg8, cg8);
+    float2 m01 = __ffma2_rn(vpa, dxa, __fmul2_rn(vpb, dxb));
+    float2 m23 = __ffma2_rn(vpc, dxc, __fmul2_rn(vpd, dxd));
+    m01 = __ffma2_rn(Sa, __ffma2_rn(g0a, cg2, __fmul2_rn(g0b, cg82)), m01);
+    m23 = __ffma2_rn(Sb, __ffma2_rn(g1a, cg2, __fmul2_rn(g1b, cg82)), m23);
     // sum over the 16 channels: channel pairs are in-thread, the 8 groups g are folded by a
     // transposing butterfly (each step halves the number of tokens a lane keeps)
     const bool b0 = (tl.g & 1) != 0, b1 = (tl.g & 2) != 0;
-    const float keep0 = b0 ? m2 : m0, keep1 = b0 ? m3 : m1;
-    const float send0 = b0 ? m0 : m2, send1 = b0 ? m1 : m3;
-    const float r0 = keep0 + __shfl_xor_sync(0xffffffffu, send0, 4);
-    const float r1 = keep1 + __shfl_xor_sync(0xffffffffu, send1, 4);
+    const float2 keepv = b0 ? m23 : m01, sendv = b0 ? m01 : m23;
+    const float2 r01 = __fadd2_rn(keepv, make_float2(__shfl_xor_sync(0xffffffffu, sendv.x, 4),
+                                                     __shfl_xor_sync(0xffffffffu, sendv.y, 4)));
+    const float r0 = r01.x, r1 = r01.y;
     const float keep = b1 ? r1 : r0, send = b1 ? r0 : r1;
     float r = keep + __shfl_xor_sync(0xffffffffu, send, 8);
     r += __shfl_xor_sync(0xffffffffu, r, 16);
