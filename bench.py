@@ -10,8 +10,11 @@ sharded over ranks and nothing is exchanged on the data path).  Rank 0 prints
 one JSON line.
 
 `value`     tokens/s with inputs resident in HBM (CUDA events around K steps).
-`e2e`       the same metric through the public `btp()` call with pinned HOST
-            buffers: H2D of coeff/x/dy and D2H of y/dx/dA inside the timed region.
+`e2e`       the same metric with pinned HOST buffers in and out, through the package's
+            host-buffer entry `btp_fwd_bwd_host` (batch slices on three streams so that
+            upload, kernels and download overlap); H2D of coeff/x/dy and D2H of y/dx/dA are
+            inside the timed region.  `via_btp_autograd` is the same through `btp()` +
+            autograd with plain copies on one stream.
 `roofline`  backward kernel (the dominant one): algorithmic bytes / its mean
             duration, measured live with CUDA events inside the timed region.
 `cpu_baseline` the CPU oracle (a restatement of the reference's PyTorch path)
@@ -282,24 +285,34 @@ def main():
         hdx.copy_(x.grad, non_blocking=True)
         hdA.copy_(a.grad, non_blocking=True)
 
-    e2e_ms = float("nan")
-    if args.e2e_steps > 0:
+    from spear_b200.ops.btp import btp_fwd_bwd_host
+
+    def e2e_step_pipelined():  # the host-buffer entry of the package: three streams, batch in slices
+        btp_fwd_bwd_host(ha, hx, hdy, hy, hdx, hdA, k=2)
+
+    def time_e2e(fn):
         for _ in range(3):
-            e2e_step()
+            fn()
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for _ in range(args.e2e_steps):
-            e2e_step()
+            fn()
         f1.record()
         barrier()
-        e2e_ms = f0.elapsed_time(f1)
+        return f0.elapsed_time(f1)
+
+    e2e_ms = e2e_autograd_ms = float("nan")
+    if args.e2e_steps > 0:
+        e2e_autograd_ms = time_e2e(e2e_step)
+        e2e_ms = time_e2e(e2e_step_pipelined)
 
     # ---- max over ranks
     if dist is not None:
         from spear_b200.sharding import max_over_ranks, sum_over_ranks
 
-        total_ms, e2e_ms, fwd_us, bwd_us = max_over_ranks([total_ms, e2e_ms, fwd_us, bwd_us], device=dev)
+        total_ms, e2e_ms, e2e_autograd_ms, fwd_us, bwd_us = max_over_ranks(
+            [total_ms, e2e_ms, e2e_autograd_ms, fwd_us, bwd_us], device=dev)
         launches = int(sum_over_ranks([launches], device=dev)[0])
 
     if rank == 0:
@@ -321,7 +334,10 @@ def main():
                 "parallelism": f"batch sharded over {world} GPU(s), no data-path collective",
             },
             "e2e": {"value": world * B * L * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "spear_b200.ops.btp.btp_fwd_bwd_host (pinned host tensors in and out, 8 batch slices on 3 streams)",
+                    "via_btp_autograd": {"value": world * B * L * args.e2e_steps / (e2e_autograd_ms * 1e-3), "unit": UNIT,
+                                         "api": "tensor.to(device) + btp() + backward() + copy_ to host, one stream"}},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "btp_backward_kernel", "achieved": bwd_gbs, "peak": peak,

@@ -484,3 +484,25 @@ def test_forward_backward_replay_from_a_cuda_graph(native):
     dA_w, dx_w = O.btp_backward(a2, x2, dy2)
     assert_limits(dx.float().cpu(), dx_w, BACKWARD_LIMITS, "dx from graph")
     assert_limits(dA.cpu(), dA_w, BACKWARD_LIMITS, "dA from graph")
+
+
+def test_host_buffer_entry_matches_device_entry(native):
+    """btp_fwd_bwd_host (pinned host tensors, sliced over three streams) == the plain device calls."""
+    from spear_b200.ops.btp import btp_fwd_bwd_host
+
+    a, x, dy = sample(21, 4, 160, 41)  # 21 batch entries in 8 slices: ragged last slice
+    pin = lambda t, dt: t.to(dt).contiguous().pin_memory()
+    ha, hx, hdy = pin(a, torch.bfloat16), pin(x, torch.bfloat16), pin(dy, torch.bfloat16)
+    hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+    hdA = torch.empty(21, 4, 160, dtype=torch.float32).pin_memory()
+    for _ in range(2):  # second call reuses the device ring
+        hy.zero_(); hdx.zero_(); hdA.zero_()
+        btp_fwd_bwd_host(ha, hx, hdy, hy, hdx, hdA, k=2)
+        torch.cuda.synchronize()
+        y = run_fwd(native, a, x)
+        dA, dx = run_bwd(native, a, x, dy)
+        assert torch.equal(hy.float(), y) and torch.equal(hdx.float(), dx) and torch.equal(hdA, dA)
+    with pytest.raises(ValueError):
+        btp_fwd_bwd_host(ha.cuda(), hx, hdy, hy, hdx, hdA)
+    with pytest.raises(ValueError):
+        btp_fwd_bwd_host(a.bfloat16(), hx, hdy, hy, hdx, hdA)  # not pinned
