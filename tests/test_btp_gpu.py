@@ -506,3 +506,31 @@ def test_host_buffer_entry_matches_device_entry(native):
         btp_fwd_bwd_host(ha.cuda(), hx, hdy, hy, hdx, hdA)
     with pytest.raises(ValueError):
         btp_fwd_bwd_host(a.bfloat16(), hx, hdy, hy, hdx, hdA)  # not pinned
+
+
+def test_more_than_65535_sequences_and_very_long_sequences(native):
+    """The reference puts B*H on grid.y (<= 65535, btp-forward.cu:490) and drops the carry beyond one cluster
+    of blocks (btp-forward.cu:359-366).  Neither limit exists here."""
+    # 70 400 sequences of two blocks
+    B, H, L = 2200, 32, 32
+    gen = torch.Generator(device="cuda").manual_seed(51)
+    x = (torch.randn(B, H, 16, L, device="cuda", generator=gen) * 0.5).bfloat16()
+    a = torch.sigmoid(torch.randn(B, H, L, device="cuda", generator=gen)).bfloat16()
+    dy = torch.randn(B, H, 16, L, device="cuda", generator=gen).bfloat16()
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    dA = torch.empty(B, H, L, device="cuda")
+    native.forward(a, x, y, None, 2, 32)
+    native.backward(a, x, dy, None, dx, dA, 2, 32)
+    idx = torch.tensor([0, 1, 1023, 2047, 2048, 2199])  # sequences on both sides of the 65 535 mark
+    a_s, x_s, dy_s = a[idx].float().cpu(), x[idx].float().cpu(), dy[idx].float().cpu()
+    assert_limits(y[idx].float().cpu(), O.btp_forward(a_s, x_s), FORWARD_LIMITS, "y")
+    dA_w, dx_w = O.btp_backward(a_s, x_s, dy_s)
+    assert_limits(dx[idx].float().cpu(), dx_w, BACKWARD_LIMITS, "dx")
+    assert_limits(dA[idx].cpu(), dA_w, BACKWARD_LIMITS, "dA")
+    # one sequence of 65 536 tokens (4096 blocks): every seam between warps carries
+    a1, x1, dy1 = sample(1, 2, 65536, 52)
+    assert_limits(run_fwd(native, a1, x1), O.btp_forward(a1, x1), FORWARD_LIMITS, "y long")
+    dA1, dx1 = run_bwd(native, a1, x1, dy1)
+    dA_w, dx_w = O.btp_backward(a1, x1, dy1)
+    assert_limits(dx1, dx_w, BACKWARD_LIMITS, "dx long")
+    assert_limits(dA1, dA_w, BACKWARD_LIMITS, "dA long")
