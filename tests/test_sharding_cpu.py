@@ -89,3 +89,44 @@ def test_reference_arm_prints_on_rank_zero_only():
     line = json.loads(outs[0])
     assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["cpu_baseline"]["kind"] == "port"
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["value"] > 0
+
+
+def _seq_worker(rank, world, port, out):
+    """Two gloo ranks, each with a slice of L; the oracle stands in for the kernels (host-side logic only)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import btp_oracle as O
+    from spear_b200.sharding import btp_sequence_parallel
+
+    g = torch.Generator().manual_seed(9)
+    B, H, L = 2, 3, 112
+    a = torch.sigmoid(torch.randn(B, H, L, generator=g, dtype=torch.float64))
+    x = torch.randn(B, H, 16, L, generator=g, dtype=torch.float64)
+    dy = torch.randn(B, H, 16, L, generator=g, dtype=torch.float64)
+    cuts = [0, 48, 112] if world == 2 else [0, 32, 64, 112]   # uneven slices
+    lo, hi = cuts[rank], cuts[rank + 1]
+    impl = (lambda c, xx, k, dt: O.btp_forward(c, xx, k, "product"),
+            lambda c, xx, d, k: O.btp_backward(c, xx, d, k, "product"))
+    al = a[..., lo:hi].clone().requires_grad_(True)
+    xl = x[..., lo:hi].clone().requires_grad_(True)
+    y = btp_sequence_parallel(al, xl, 2, torch.float64, None, impl)
+    y.backward(dy[..., lo:hi])
+    y_full = O.btp_forward(a, x, 2, "product")
+    dA_full, dx_full = O.btp_backward(a, x, dy, 2, "product")
+    res = {
+        "y": (y.detach() - y_full[..., lo:hi]).abs().max().item(),
+        "dx": (xl.grad - dx_full[..., lo:hi]).abs().max().item(),
+        "dA": (al.grad - dA_full[..., lo:hi]).abs().max().item(),
+    }
+    json.dump(res, open(f"{out}.{rank}", "w"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_sharding_with_halo_exchange(tmp_path, world):
+    out = str(tmp_path / "seq")
+    mp.spawn(_seq_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    for rank in range(world):
+        res = json.load(open(f"{out}.{rank}"))
+        assert max(res.values()) < 1e-12, (rank, res)
