@@ -15,12 +15,15 @@
 // How it is mapped to the machine:
 //   * Work unit = a chunk of TL = 64*NBOX tokens of one sequence: x as NBOX TMA boxes of
 //     [16 channels x 64 tokens] bf16 (128-byte swizzle), the coefficients as one bulk copy.
-//   * Every WARP owns a private ring of STAGES chunk buffers with its own mbarriers and walks a
-//     contiguous range of chunks.  No block-wide or grid-wide synchronisation exists, so no warp
-//     ever waits for another warp; the only waits are on the warp's own TMA loads (bounded).
+//   * Every WARP owns a private ring of STAGES chunk buffers with its own mbarriers and walks its
+//     own list of chunks (whole sequences dealt round-robin when there are many, else a contiguous
+//     range).  No block-wide or grid-wide synchronisation exists, so no warp ever waits for another
+//     warp; the only waits are on the warp's own TMA loads (bounded).
 //   * Once per chunk the warp turns the coefficients into the per-token tables the blocks need
 //     (T, P, and for backward P shifted by one token and the last Lmat row), so that the per-block
 //     work is the Lmat fragment (6 exponentials per lane), the tensor-core products and FMAs.
+//   * Lmat goes to the tensor cores as two bf16 terms (hi + lo), which reproduces the fp32 matrix to
+//     ~2^-17; the per-block fp32 arithmetic of the backward uses packed fp32x2 instructions.
 //   * The carry stays in registers while a warp walks along a sequence.  Where a warp's range
 //     starts (ends) inside a sequence the neighbouring block is re-read from global memory
 //     (16x16 values, a "halo") and its carry (dCarry) recomputed, so no seam ever drops a carry.
