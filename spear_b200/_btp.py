@@ -91,6 +91,8 @@ def forward(coeff, x, y, checkpoint, k: int, wpb: int, *, log_coeff: bool = Fals
         _require(tuple(checkpoint.shape) == (B, H, L // BLK, DH), "checkpoint must be [B, H, L/16, 16]")
     ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
     _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
+    if x.numel() == 0:  # nothing to compute (empty batch, no heads or no tokens)
+        return
     with _OnDevice(x.device.index) as stream:
         rc = _lib.load().btp_sm100_forward(
             _ptr(coeff), _ptr(x), _ptr(y), _ptr(checkpoint), B, H, L, int(k), ctag, _TAG[y.dtype], ctypes.c_void_p(stream)
@@ -107,6 +109,8 @@ def backward(coeff, x, dy, checkpoint, dx, dA, k: int, wpb: int, *, log_coeff: b
     _require(tuple(dA.shape) == (B, H, L) and dA.dtype == torch.float32 and dA.is_contiguous(), "dA must be float32 [B, H, L]")
     ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
     _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
+    if x.numel() == 0:
+        return
     with _OnDevice(x.device.index) as stream:
         rc = _lib.load().btp_sm100_backward(
             _ptr(coeff), _ptr(x), _ptr(dy), _ptr(None), _ptr(dx), _ptr(dA), B, H, L, int(k), ctag, _TAG[dy.dtype],

@@ -48,7 +48,7 @@ def bench_gated(B, L, H, steps, sets):
     def fwd():
         al, bl, c, v, do, out = data[i[0] % sets]
         i[0] += 1
-        G._forward_impl(al, bl, c, v, out, 2)
+        G._launch_forward(al, bl, c, v, out, 2)
 
     def bwd():
         al, bl, c, v, do, out = data[i[0] % sets]

@@ -15,6 +15,7 @@ import torch
 
 from ... import _btp as _native
 from ... import _lib
+from . import interface as _iface
 
 __all__ = ["gated_btp", "gated_btp_wide", "gated_btp_supported"]
 
@@ -36,7 +37,7 @@ def _rows(t: torch.Tensor, cols: int, what: str) -> int:
     return t.stride(1)
 
 
-def _forward_impl(a_logits, b_logits, c, v, out, k: int) -> None:
+def _launch_forward(a_logits, b_logits, c, v, out, k: int) -> None:
     B, L, H = a_logits.shape
     cols = H * 16
     ld_a = _rows(a_logits, H, "a_logits")
@@ -64,7 +65,7 @@ class _GatedBTP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a_logits, b_logits, c, v, k):
         out = torch.empty(v.shape, device=v.device, dtype=v.dtype)
-        _forward_impl(a_logits, b_logits, c, v, out, k)
+        torch.ops.spear_btp.gated_forward(a_logits, b_logits, c, v, out, int(k))
         ctx.save_for_backward(a_logits, b_logits, c, v)
         ctx.k = int(k)
         return out
@@ -80,20 +81,59 @@ class _GatedBTP(torch.autograd.Function):
 _FUSED_BACKWARD = True  # False: the op's own backward kernel between elementwise CUDA passes (for comparison)
 
 
+def _launch_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, k: int) -> None:
+    B, L, H = a_logits.shape
+    cols = H * 16
+    ld = [_rows(a_logits, H, "a_logits")] + [_rows(t, cols, n) for t, n in
+                                             ((b_logits, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"))]
+    ld += [_rows(da, H, "da_logits")] + [_rows(t, cols, n) for t, n in ((db, "db_logits"), (dc, "dc"), (dv, "dv"))]
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    with _native._OnDevice(v.device.index) as stream:
+        rc = _lib.load().btp_sm100_gated_backward(p(a_logits), p(b_logits), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
+                                                  B, L, H, *ld, int(k), ctypes.c_void_p(stream))
+    _lib.check(rc, "btp_sm100_gated_backward")
+
+
+# ---- custom ops (mutating, with no-op fakes) so that torch.compile traces through them like through
+#      spear_btp::forward / spear_btp::backward
+def _op_gated_forward(a_logits: torch.Tensor, b_logits: torch.Tensor, c: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                      k: int) -> None:
+    _launch_forward(a_logits, b_logits, c, v, out, k)
+
+
+def _op_gated_backward(a_logits: torch.Tensor, b_logits: torch.Tensor, c: torch.Tensor, v: torch.Tensor, dout: torch.Tensor,
+                       da: torch.Tensor, db: torch.Tensor, dc: torch.Tensor, dv: torch.Tensor, k: int) -> None:
+    _launch_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, k)
+
+
+def _op_gated_forward_wide(wide: torch.Tensor, out: torch.Tensor, heads: int, k: int) -> None:
+    bl, c, v, al = _split_wide(wide, heads)
+    _launch_forward(al, bl, c, v, out, k)
+
+
+def _op_gated_backward_wide(wide: torch.Tensor, dout: torch.Tensor, dwide: torch.Tensor, heads: int, k: int) -> None:
+    bl, c, v, al = _split_wide(wide, heads)
+    db, dc, dv, da = _split_wide(dwide, heads)
+    _launch_backward(al, bl, c, v, dout, da, db, dc, dv, k)
+
+
+def _fake(*args) -> None:
+    return None
+
+
+_iface._register(_iface._LIB, "spear_btp", "gated_forward", _op_gated_forward, _fake, ["out"])
+_iface._register(_iface._LIB, "spear_btp", "gated_backward", _op_gated_backward, _fake, ["da", "db", "dc", "dv"])
+_iface._register(_iface._LIB, "spear_btp", "gated_forward_wide", _op_gated_forward_wide, _fake, ["out"])
+_iface._register(_iface._LIB, "spear_btp", "gated_backward_wide", _op_gated_backward_wide, _fake, ["dwide"])
+
+
 def _backward_fused(a_logits, b_logits, c, v, dout, k):
     B, L, H = a_logits.shape
     cols = H * 16
     dout = dout if dout.stride(2) == 1 else dout.contiguous()
     da = torch.empty(B, L, H, device=v.device, dtype=v.dtype)
     db, dc, dv = (torch.empty(B, L, cols, device=v.device, dtype=v.dtype) for _ in range(3))
-    ld = [_rows(a_logits, H, "a_logits")] + [_rows(t, cols, n) for t, n in
-                                             ((b_logits, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"))]
-    ld += [H, cols, cols, cols]
-    p = lambda t: ctypes.c_void_p(t.data_ptr())
-    with _native._OnDevice(v.device.index) as stream:
-        rc = _lib.load().btp_sm100_gated_backward(p(a_logits), p(b_logits), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
-                                                  B, L, H, *ld, int(k), ctypes.c_void_p(stream))
-    _lib.check(rc, "btp_sm100_gated_backward")
+    torch.ops.spear_btp.gated_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, int(k))
     return da, db, dc, dv
 
 
@@ -130,9 +170,9 @@ class _GatedBTPWide(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, wide, heads, k):
-        bl, c, v, al = _split_wide(wide, heads)
-        out = torch.empty(v.shape, device=v.device, dtype=v.dtype)
-        _forward_impl(al, bl, c, v, out, k)
+        B, L, _ = wide.shape
+        out = torch.empty(B, L, heads * 16, device=wide.device, dtype=wide.dtype)
+        torch.ops.spear_btp.gated_forward_wide(wide, out, int(heads), int(k))
         ctx.save_for_backward(wide)
         ctx.heads, ctx.k = int(heads), int(k)
         return out
@@ -140,20 +180,9 @@ class _GatedBTPWide(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         (wide,) = ctx.saved_tensors
-        H, k = ctx.heads, ctx.k
-        bl, c, v, al = _split_wide(wide, H)
         dwide = torch.empty_like(wide)
-        db, dc, dv, da = _split_wide(dwide, H)
         dout = dout if dout.stride(2) == 1 else dout.contiguous()
-        B, L, _ = al.shape
-        cols = H * 16
-        ld = [_rows(al, H, "a_logits")] + [_rows(t, cols, n) for t, n in ((bl, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"))]
-        ld += [_rows(da, H, "da_logits")] + [_rows(t, cols, n) for t, n in ((db, "db"), (dc, "dc"), (dv, "dv"))]
-        p = lambda t: ctypes.c_void_p(t.data_ptr())
-        with _native._OnDevice(v.device.index) as stream:
-            rc = _lib.load().btp_sm100_gated_backward(p(al), p(bl), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
-                                                      B, L, H, *ld, k, ctypes.c_void_p(stream))
-        _lib.check(rc, "btp_sm100_gated_backward")
+        torch.ops.spear_btp.gated_backward_wide(wide, dout, dwide, ctx.heads, ctx.k)
         return dwide, None, None
 
 

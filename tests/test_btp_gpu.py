@@ -534,3 +534,42 @@ def test_more_than_65535_sequences_and_very_long_sequences(native):
     dA_w, dx_w = O.btp_backward(a1, x1, dy1)
     assert_limits(dx1, dx_w, BACKWARD_LIMITS, "dx long")
     assert_limits(dA1, dA_w, BACKWARD_LIMITS, "dA long")
+
+
+def test_empty_inputs(native):
+    """Empty batch / no tokens: nothing is launched, shapes and dtypes are kept, gradients are empty."""
+    from spear_b200.ops.btp import btp
+
+    for shape in ((0, 4, 64), (2, 4, 0)):
+        B, H, L = shape
+        a = torch.zeros(B, H, L, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        x = torch.zeros(B, H, 16, L, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        y = btp(a, x, output_dtype=torch.bfloat16)
+        assert y.shape == x.shape and y.dtype == torch.bfloat16
+        y.sum().backward()
+        assert a.grad.shape == a.shape and x.grad.shape == x.shape
+
+
+def test_op_and_layer_under_torch_compile(native):
+    """The reference's tests compile both the op and the layer (tests/btp/test_numerics.py:50-55,
+    tests/phalanx/test_phalanx_numerics.py:64-69): every kernel here is a registered custom op, so dynamo
+    captures one graph around them."""
+    from spear_b200.nn.phalanx import Phalanx
+    from spear_b200.ops.btp import btp
+
+    a, x, _ = sample(2, 8, 128, 61)
+    ad, xd = dev(a, torch.bfloat16), dev(x, torch.bfloat16)
+    want = btp(ad, xd, output_dtype=torch.bfloat16)
+    got = torch.compile(btp, fullgraph=True)(ad, xd, output_dtype=torch.bfloat16)  # default backend
+    assert torch.equal(got, want)
+
+    torch.manual_seed(7)
+    layer = Phalanx(dim=128, length=64, dtype=torch.bfloat16).cuda()
+    u = torch.randn(2, 64, 128, device="cuda")
+    want = layer(u)
+    compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")
+    ui = u.clone().requires_grad_(True)
+    got = compiled(ui)
+    assert O.rel_l2(got.float().cpu(), want.float().cpu()) <= 1e-2
+    got.sum().backward()
+    assert torch.isfinite(ui.grad).all() and ui.grad.abs().sum() > 0
