@@ -196,10 +196,12 @@ def main():
         args.warmup = 3
     torch.cuda.set_device(local_rank)
     dist = None
+    # Rank 0's stdout carries exactly one JSON line.  Libraries write banners to file descriptor 1 (NCCL
+    # prints its version there), so everything else that lands on it during the run is sent to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        # rank 0's stdout carries exactly one JSON line: keep NCCL's version banner off it
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO"):
-            os.environ["NCCL_DEBUG"] = "WARN"
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -358,7 +360,7 @@ def main():
                 "value": nb * L / min(times), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                 "sample": f"{nb}/{B} batch entries, fwd+bwd float32 torch CPU autograd, best of 3 after 1 warm-up",
             }
-        print(json.dumps(line), flush=True)
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         dist.destroy_process_group()
 
