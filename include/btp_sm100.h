@@ -134,6 +134,40 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
                              long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_do,
                              long long ld_da, long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream);
 
+/*
+ * One decode step of the streaming form of the recurrence, all of it in one launch.
+ * Replaces the tensor-op body of step_jagged (spear/nn/phalanx/inference.py:177-266).
+ *   a_t                      [n_heads]      gate of the new token (its natural log when gate_is_log)
+ *   x_t, c_t, v_t, y_t       [n_heads,16]   n_heads = B*H, rows contiguous
+ *   h_loc, c_prev_loc        [n_heads,16]   state going in (JagState.h_loc, .c_prev_loc)
+ *   r_pref                   [n_heads]      state going in: running gate product of the current block, or its
+ *                                           log when r_is_log; NULL stands for an empty block (1, or log 1)
+ *   h_loc_out, r_pref_out    state coming out, separate buffers (the reference returns a new state object and
+ *                            leaves the old one valid); passing the input pointers updates in place
+ *   c_prev_loc_out           written only when block_complete (the step with in-block index 15); may be NULL
+ *                            otherwise - c_prev_loc carries over unchanged
+ *   dtype                    storage of the [n_heads,16] tensors, gate_dtype that of a_t and r_pref:
+ *                            BTP_DTYPE_BF16 | BTP_DTYPE_F32.  Arithmetic is fp32; one rounding on the store.
+ *   y = (h + r * c_prev_loc) * c_t + v_t  with  h = a * h_loc + x_t,  r = a * r_pref
+ *   (log space: r = exp(r_pref + log(max(a, tiny)))).
+ */
+int btp_sm100_decode_step(const void* a_t, const void* x_t, const void* c_t, const void* v_t, void* y_t,
+                          const void* h_loc, const void* r_pref, const void* c_prev_loc, void* h_loc_out,
+                          void* r_pref_out, void* c_prev_loc_out, long long n_heads, int block_complete,
+                          int gate_is_log, int r_is_log, int dtype, int gate_dtype, void* stream);
+
+/*
+ * Hand-off state after a prompt of L tokens (any L >= 1), one launch.
+ * Replaces the state extraction at the end of parallel_jagged (spear/nn/phalanx/inference.py:333-358), which
+ * there falls out of two nested Python loops over the whole prompt; the state only depends on the last
+ * (possibly partial) 16-token block and the complete block before it.
+ *   a   [n_heads, L]      gates (log gates when gate_is_log), contiguous
+ *   x   [n_heads, 16, L]  driving term, contiguous
+ *   h_loc, c_prev_loc [n_heads,16], r_pref [n_heads]: outputs (r_pref always in linear space, as the reference's)
+ */
+int btp_sm100_prefill_state(const void* a, const void* x, void* h_loc, void* r_pref, void* c_prev_loc, long long n_heads,
+                            int L, int gate_is_log, int dtype, int gate_dtype, void* stream);
+
 /* Name of a status code ("BTP_OK", "BTP_ERR_BAD_SHAPE", ...).  Never NULL. */
 const char* btp_sm100_status_string(int status);
 

@@ -117,3 +117,52 @@ def backward(coeff, x, dy, checkpoint, dx, dA, k: int, wpb: int, *, log_coeff: b
             ctypes.c_void_p(stream),
         )
     _lib.check(rc, "btp_sm100_backward")
+
+
+def decode_step(a_t, x_t, c_t, v_t, y_t, h_loc, r_pref, c_prev_loc, h_loc_out, r_pref_out, c_prev_loc_out, *,
+                block_complete: bool, gate_is_log: bool, r_is_log: bool) -> None:
+    """One streaming step in one launch (btp_sm100_decode_step).  No counterpart in ``spear._btp``: the reference
+    does this with tensor ops (spear/nn/phalanx/inference.py:177-266).  All tensors contiguous, [.., 16] ones of one
+    dtype (bfloat16 or float32), a_t / r_pref / r_pref_out of one dtype (bfloat16 or float32)."""
+    big = (x_t, c_t, v_t, y_t, h_loc, c_prev_loc, h_loc_out) + (() if c_prev_loc_out is None else (c_prev_loc_out,))
+    small = (a_t, r_pref_out) + (() if r_pref is None else (r_pref,))
+    _require(all(t.is_cuda for t in big + small), "decode_step needs CUDA tensors (there is no CPU path)")
+    _require(x_t.dim() >= 1 and x_t.shape[-1] == DH, f"x_t must be [..., {DH}]")
+    _require(all(t.shape == x_t.shape and t.dtype == x_t.dtype and t.is_contiguous() for t in big),
+             "x_t, c_t, v_t, y_t and the [.,16] states must share shape and dtype and be contiguous")
+    _require(all(t.shape == x_t.shape[:-1] and t.dtype == a_t.dtype and t.is_contiguous() for t in small),
+             "a_t and the r_pref states must be [...] of one dtype and contiguous")
+    _require(x_t.dtype in _TAG and a_t.dtype in _TAG, "decode_step takes bfloat16 or float32 tensors")
+    _require(not block_complete or c_prev_loc_out is not None, "the step that completes a block writes c_prev_loc_out")
+    n_heads = a_t.numel()
+    if n_heads == 0:
+        return
+    with _OnDevice(x_t.device.index) as stream:
+        rc = _lib.load().btp_sm100_decode_step(
+            _ptr(a_t), _ptr(x_t), _ptr(c_t), _ptr(v_t), _ptr(y_t), _ptr(h_loc), _ptr(r_pref), _ptr(c_prev_loc),
+            _ptr(h_loc_out), _ptr(r_pref_out), _ptr(c_prev_loc_out), n_heads, int(block_complete), int(gate_is_log),
+            int(r_is_log), _TAG[x_t.dtype], _TAG[a_t.dtype], ctypes.c_void_p(stream),
+        )
+    _lib.check(rc, "btp_sm100_decode_step")
+
+
+def prefill_state(a, x, h_loc, r_pref, c_prev_loc, *, gate_is_log: bool) -> None:
+    """Hand-off state after a prompt (btp_sm100_prefill_state; spear/nn/phalanx/inference.py:333-358).
+    a [B,H,L], x [B,H,16,L] contiguous; outputs [B,H,16], [B,H], [B,H,16]."""
+    _require(all(t.is_cuda for t in (a, x, h_loc, r_pref, c_prev_loc)), "prefill_state needs CUDA tensors (there is no CPU path)")
+    _require(x.dim() == 4 and x.shape[2] == DH, f"x must be [B, H, {DH}, L]")
+    B, H, _, L = x.shape
+    _require(tuple(a.shape) == (B, H, L) and a.is_contiguous() and x.is_contiguous(), "a must be contiguous [B, H, L], x contiguous")
+    _require(L >= 1, "the prompt must hold at least one token")
+    for t in (h_loc, c_prev_loc):
+        _require(tuple(t.shape) == (B, H, DH) and t.dtype == x.dtype and t.is_contiguous(), "h_loc, c_prev_loc must be [B, H, 16] of x's dtype")
+    _require(tuple(r_pref.shape) == (B, H) and r_pref.dtype == a.dtype and r_pref.is_contiguous(), "r_pref must be [B, H] of a's dtype")
+    _require(x.dtype in _TAG and a.dtype in _TAG, "prefill_state takes bfloat16 or float32 tensors")
+    if B * H == 0:
+        return
+    with _OnDevice(x.device.index) as stream:
+        rc = _lib.load().btp_sm100_prefill_state(
+            _ptr(a), _ptr(x), _ptr(h_loc), _ptr(r_pref), _ptr(c_prev_loc), B * H, L, int(gate_is_log),
+            _TAG[x.dtype], _TAG[a.dtype], ctypes.c_void_p(stream),
+        )
+    _lib.check(rc, "btp_sm100_prefill_state")

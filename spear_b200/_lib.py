@@ -29,6 +29,8 @@ SYMBOLS = {
     "btp_sm100_forward_noalloc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_gated_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _vp]),
     "btp_sm100_gated_backward": (_i, [_vp] * 9 + [_i, _i, _i] + [_ll] * 9 + [_i, _vp]),
+    "btp_sm100_decode_step": (_i, [_vp] * 11 + [_ll, _i, _i, _i, _i, _i, _vp]),
+    "btp_sm100_prefill_state": (_i, [_vp] * 5 + [_ll, _i, _i, _i, _i, _vp]),
     "btp_sm100_status_string": (ctypes.c_char_p, [_i]),
     "btp_sm100_last_error": (ctypes.c_char_p, []),
     "btp_sm100_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_uint)]),

@@ -20,6 +20,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libbtp_sm100.so")
 SOURCES = [os.path.join(CSRC, "btp_sm100.cu")]
 HEADERS = [
     os.path.join(CSRC, "btp_kernels.cuh"),
+    os.path.join(CSRC, "btp_decode.cuh"),
     os.path.join(CSRC, "btp_gated.cuh"),
     os.path.join(CSRC, "btp_gated_bwd.cuh"),
     os.path.join(CSRC, "btp_ptx.cuh"),

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "btp_decode.cuh"
 #include "btp_gated.cuh"
 #include "btp_gated_bwd.cuh"
 #include "btp_kernels.cuh"
@@ -414,6 +415,28 @@ int noalloc_scratch(float** out) {
 }  // namespace
 
 // ====================================================================== C ABI
+namespace {
+template <class T, class TA>
+int launch_decode_step(const btp::DecodeParams& p, cudaStream_t s) {
+  const long long quads = p.n_heads * 4;
+  const long long blocks = (quads + 255) / 256;
+  btp::btp_decode_step_kernel<T, TA><<<static_cast<unsigned>(blocks), 256, 0, s>>>(p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+template <class T, class TA>
+int launch_prefill_state(const btp::PrefillStateParams& p, cudaStream_t s) {
+  const long long threads = p.n_heads * 16;
+  const long long blocks = (threads + 255) / 256;
+  btp::btp_prefill_state_kernel<T, TA><<<static_cast<unsigned>(blocks), 256, 0, s>>>(p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+bool bad_tag(int t) { return t != BTP_DTYPE_BF16 && t != BTP_DTYPE_F32; }
+}  // namespace
+
 extern "C" {
 
 int btp_sm100_forward(const void* coeff, const void* x, void* y, float* checkpoint, int B, int H, int L, int k,
@@ -569,6 +592,74 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
+}
+
+int btp_sm100_decode_step(const void* a_t, const void* x_t, const void* c_t, const void* v_t, void* y_t,
+                          const void* h_loc, const void* r_pref, const void* c_prev_loc, void* h_loc_out,
+                          void* r_pref_out, void* c_prev_loc_out, long long n_heads, int block_complete,
+                          int gate_is_log, int r_is_log, int dtype, int gate_dtype, void* stream) {
+  const char* fn = "btp_sm100_decode_step";
+  if (n_heads <= 0 || n_heads > (1ll << 40)) return fail(BTP_ERR_BAD_SHAPE, "%s: n_heads must be in [1, 2^40] (got %lld)", fn, n_heads);
+  if (bad_tag(dtype) || bad_tag(gate_dtype))
+    return fail(BTP_ERR_BAD_DTYPE, "%s: dtype and gate_dtype must be BTP_DTYPE_BF16 or BTP_DTYPE_F32", fn);
+  if (!a_t || !x_t || !c_t || !v_t || !y_t || !h_loc || !c_prev_loc || !h_loc_out || !r_pref_out)
+    return fail(BTP_ERR_NULL_POINTER, "%s: only r_pref and (unless the block completes) c_prev_loc_out may be NULL", fn);
+  if (block_complete && !c_prev_loc_out)
+    return fail(BTP_ERR_NULL_POINTER, "%s: c_prev_loc_out is needed on the step that completes a block", fn);
+  if (misaligned(x_t) || misaligned(c_t) || misaligned(v_t) || misaligned(y_t) || misaligned(h_loc) || misaligned(c_prev_loc) ||
+      misaligned(h_loc_out) || (c_prev_loc_out && misaligned(c_prev_loc_out)))
+    return fail(BTP_ERR_MISALIGNED, "%s: the [n_heads,16] tensors must be 16-byte aligned", fn);
+  const unsigned amask = gate_dtype == BTP_DTYPE_F32 ? 3u : 1u;
+  if ((reinterpret_cast<uintptr_t>(a_t) & amask) || (reinterpret_cast<uintptr_t>(r_pref_out) & amask) ||
+      (r_pref && (reinterpret_cast<uintptr_t>(r_pref) & amask)))
+    return fail(BTP_ERR_MISALIGNED, "%s: a gate pointer is not aligned to its element size", fn);
+  if ((n_heads * 4 + 255) / 256 > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: too many heads for one launch", fn);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  btp::DecodeParams p{};
+  p.a = a_t; p.x = x_t; p.c = c_t; p.v = v_t; p.y = y_t;
+  p.h_in = h_loc; p.r_in = r_pref; p.cprev = c_prev_loc;
+  p.h_out = h_loc_out; p.r_out = r_pref_out; p.cprev_out = c_prev_loc_out;
+  p.n_heads = n_heads;
+  p.a_log = gate_is_log != 0;
+  p.r_log = r_is_log != 0;
+  p.block_done = block_complete != 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == BTP_DTYPE_BF16)
+    return gate_dtype == BTP_DTYPE_BF16 ? launch_decode_step<__nv_bfloat16, __nv_bfloat16>(p, s)
+                                        : launch_decode_step<__nv_bfloat16, float>(p, s);
+  return gate_dtype == BTP_DTYPE_BF16 ? launch_decode_step<float, __nv_bfloat16>(p, s) : launch_decode_step<float, float>(p, s);
+}
+
+int btp_sm100_prefill_state(const void* a, const void* x, void* h_loc, void* r_pref, void* c_prev_loc, long long n_heads,
+                            int L, int gate_is_log, int dtype, int gate_dtype, void* stream) {
+  const char* fn = "btp_sm100_prefill_state";
+  if (n_heads <= 0 || L <= 0 || n_heads > (1ll << 36))
+    return fail(BTP_ERR_BAD_SHAPE, "%s: n_heads and L must be positive (got %lld, %d)", fn, n_heads, L);
+  if (bad_tag(dtype) || bad_tag(gate_dtype))
+    return fail(BTP_ERR_BAD_DTYPE, "%s: dtype and gate_dtype must be BTP_DTYPE_BF16 or BTP_DTYPE_F32", fn);
+  if (!a || !x || !h_loc || !r_pref || !c_prev_loc) return fail(BTP_ERR_NULL_POINTER, "%s: no pointer may be NULL", fn);
+  const unsigned xmask = dtype == BTP_DTYPE_F32 ? 3u : 1u;
+  const unsigned amask = gate_dtype == BTP_DTYPE_F32 ? 3u : 1u;
+  if ((reinterpret_cast<uintptr_t>(x) & xmask) || (reinterpret_cast<uintptr_t>(h_loc) & xmask) ||
+      (reinterpret_cast<uintptr_t>(c_prev_loc) & xmask) || (reinterpret_cast<uintptr_t>(a) & amask) ||
+      (reinterpret_cast<uintptr_t>(r_pref) & amask))
+    return fail(BTP_ERR_MISALIGNED, "%s: a pointer is not aligned to its element size", fn);
+  if ((n_heads * 16 + 255) / 256 > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: too many heads for one launch", fn);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  btp::PrefillStateParams p{};
+  p.a = a; p.x = x; p.h_loc = h_loc; p.r_pref = r_pref; p.cprev = c_prev_loc;
+  p.n_heads = n_heads; p.L = L; p.a_log = gate_is_log != 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == BTP_DTYPE_BF16)
+    return gate_dtype == BTP_DTYPE_BF16 ? launch_prefill_state<__nv_bfloat16, __nv_bfloat16>(p, s)
+                                        : launch_prefill_state<__nv_bfloat16, float>(p, s);
+  return gate_dtype == BTP_DTYPE_BF16 ? launch_prefill_state<float, __nv_bfloat16>(p, s) : launch_prefill_state<float, float>(p, s);
 }
 
 const char* btp_sm100_status_string(int status) {

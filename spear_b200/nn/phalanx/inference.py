@@ -3,9 +3,9 @@
 Mirror of the reference's streaming helpers (spear/nn/phalanx/inference.py:142-360): the same ``JagState``
 fields, ``parallel_jagged`` (prompt prefill returning the outputs and the hand-off state) and
 ``step_jagged`` (one decode step).  The reference runs two nested Python loops over blocks and tokens for
-the prefill; here the prompt goes through the BTP forward kernel in one launch and only the hand-off state,
-which depends on at most the last 32 tokens, is formed with a few small tensor ops.  The decode step is a
-handful of elementwise device ops on [B, H, 16] tensors.  CUDA tensors only; block_len must be 16.
+the prefill; here the prompt goes through the BTP forward kernel in one launch, the hand-off state (which
+depends on at most the last 32 tokens) comes from one small kernel, and a decode step is one kernel launch
+instead of a dozen tensor ops.  CUDA tensors only - there is no CPU path; block_len must be 16.
 """
 
 from __future__ import annotations
@@ -45,15 +45,19 @@ class JagState:
         )
 
 
-def _local_tail(a_blk: torch.Tensor, x_blk: torch.Tensor):
-    """Zero-initialised scan over one (possibly partial) block: last local value (B,H,D) and gate product (B,H)."""
-    h = torch.zeros(x_blk.shape[:-1], dtype=torch.float32, device=x_blk.device)
-    r = torch.ones(a_blk.shape[:-1], dtype=torch.float32, device=a_blk.device)
-    for k in range(a_blk.shape[-1]):  # at most 16 steps on [B,H,D] tensors
-        ak = a_blk[..., k].float()
-        h = ak.unsqueeze(-1) * h + x_blk[..., k].float()
-        r = r * ak
-    return h, r
+_KERNEL_DTYPES = (torch.bfloat16, torch.float32)
+
+
+def _kernel_dtype(*tensors):
+    """Storage type the kernels run in: the promoted type if it is bfloat16 or float32, else float32."""
+    dt = tensors[0].dtype
+    for t in tensors[1:]:
+        dt = torch.promote_types(dt, t.dtype)
+    return dt, (dt if dt in _KERNEL_DTYPES else torch.float32)
+
+
+def _as(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    return t.to(dtype).contiguous()
 
 
 @torch.no_grad()
@@ -70,9 +74,10 @@ def parallel_jagged(A, X, C, V, *, block_len: int, use_log_a: bool = False):
     Bsz, H, D, L = V.shape
     if D != 16:
         raise ValueError("head_dim must be 16")
+    if L < 1:
+        raise ValueError("the prompt must hold at least one token")
     pad = (-L) % BLOCK
-    a_lin = A.float().exp() if use_log_a else A.float()
-    coeff = A.float() if use_log_a else a_lin
+    coeff = A.float()
     x = X.to(torch.bfloat16)
     if pad:
         coeff = torch.nn.functional.pad(coeff, (0, pad), value=0.0 if use_log_a else 1.0)
@@ -83,46 +88,49 @@ def parallel_jagged(A, X, C, V, *, block_len: int, use_log_a: bool = False):
     _native.forward(coeff, x, y, None, 2, 32, log_coeff=use_log_a)
     Y = (y[..., :L] * C.float() + V.float()).to(V.dtype)
 
-    # hand-off state (inference.py:333-358): it depends on the last partial block and the last complete one
-    n_completed = L // BLOCK
-    tail_i = (L - 1) % BLOCK
-    s_last = (L - 1) // BLOCK * BLOCK
-    h_tail, r_tail = _local_tail(a_lin[..., s_last:L], X[..., s_last:L])
-    if tail_i == BLOCK - 1:
-        c_prev_tail = h_tail.clone()
-        r_tail = torch.ones_like(r_tail)
-        i_next = 0
-    else:
-        if n_completed > 0:
-            c_prev_tail, _ = _local_tail(a_lin[..., s_last - BLOCK:s_last], X[..., s_last - BLOCK:s_last])
-        else:
-            c_prev_tail = torch.zeros_like(h_tail)
-        i_next = tail_i + 1
-    state = JagState(h_loc=h_tail.to(V.dtype), r_pref=r_tail.to(a_lin.dtype if A.dtype == torch.float32 else A.dtype),
-                     c_prev_loc=c_prev_tail.to(V.dtype), i=i_next, block_len=block_len, use_log_r=False, log_r_pref=None)
+    # hand-off state (inference.py:333-358): one launch over the last partial block and the complete one before it
+    _, xdt = _kernel_dtype(X)
+    _, adt = _kernel_dtype(A)
+    h_tail = torch.empty((Bsz, H, D), device=X.device, dtype=xdt)
+    c_prev_tail = torch.empty_like(h_tail)
+    r_tail = torch.empty((Bsz, H), device=X.device, dtype=adt)
+    _native.prefill_state(_as(A, adt), _as(X, xdt), h_tail, r_tail, c_prev_tail, gate_is_log=use_log_a)
+    state = JagState(h_loc=h_tail.to(V.dtype), r_pref=r_tail.to(A.dtype), c_prev_loc=c_prev_tail.to(V.dtype),
+                     i=(L % BLOCK), block_len=block_len, use_log_r=False, log_r_pref=None)
     return Y, state
 
 
 @torch.no_grad()
 def step_jagged(A_t, X_t, C_t, V_t, state: JagState, *, use_log_a: bool = False):
-    """One decode step (inference.py:177-266): returns (y_t [B,H,D], new JagState)."""
-    a_t = A_t.exp() if use_log_a else A_t
-    h_loc = a_t.unsqueeze(-1) * state.h_loc + X_t
-    log_space = state.use_log_r or use_log_a
-    if log_space:
-        tiny = torch.finfo(a_t.dtype).tiny
-        prev = state.log_r_pref if state.log_r_pref is not None else torch.zeros_like(a_t)
-        log_r = prev + torch.log(a_t.clamp_min(tiny))
-        r_pref = torch.exp(log_r)
-    else:
-        prev = state.r_pref if state.r_pref is not None else torch.ones_like(a_t)
-        r_pref = a_t * prev
-        log_r = None
-    y_t = (h_loc + r_pref.unsqueeze(-1) * state.c_prev_loc) * C_t + V_t
-    i_next = state.i + 1
-    if i_next == state.block_len:  # block complete: freeze its last local value, start the next block empty
-        return y_t, JagState(h_loc=torch.zeros_like(h_loc), r_pref=None if log_space else torch.ones_like(A_t),
-                             c_prev_loc=h_loc.clone(), i=0, block_len=state.block_len, use_log_r=log_space,
-                             log_r_pref=torch.zeros_like(A_t) if log_space else None)
-    return y_t, JagState(h_loc=h_loc, r_pref=None if log_space else r_pref, c_prev_loc=state.c_prev_loc, i=i_next,
-                         block_len=state.block_len, use_log_r=log_space, log_r_pref=log_r if log_space else None)
+    """One decode step (inference.py:177-266): returns (y_t [B,H,D], new JagState).
+
+    One kernel launch.  Like the reference it returns fresh state tensors and leaves `state` valid; the frozen
+    `c_prev_loc` is shared between consecutive states until a block completes.  Arithmetic is fp32 with a single
+    rounding to the storage type, where the reference rounds after every tensor op.
+    """
+    if not (A_t.is_cuda and X_t.is_cuda):
+        raise RuntimeError("step_jagged needs CUDA tensors: this package has no CPU path")
+    if state.block_len != BLOCK:
+        raise NotImplementedError(f"the kernel's block length is {BLOCK} (got block_len={state.block_len})")
+    log_space = bool(state.use_log_r or use_log_a)
+    r_prev = state.log_r_pref if log_space else state.r_pref
+    out_dt, dt = _kernel_dtype(X_t, C_t, V_t, state.h_loc, state.c_prev_loc)
+    gate_out_dt, gdt = _kernel_dtype(*((A_t,) if r_prev is None else (A_t, r_prev)))
+    a_t, x_t, c_t, v_t = _as(A_t, gdt), _as(X_t, dt), _as(C_t, dt), _as(V_t, dt)
+    h_in, cp_in = _as(state.h_loc, dt), _as(state.c_prev_loc, dt)
+    r_in = None if r_prev is None else _as(r_prev, gdt)
+    done = state.i + 1 == state.block_len
+    y_t = torch.empty_like(x_t)
+    h_out = torch.empty_like(x_t)
+    r_out = torch.empty_like(a_t)
+    cp_out = torch.empty_like(x_t) if done else None
+    _native.decode_step(a_t, x_t, c_t, v_t, y_t, h_in, r_in, cp_in, h_out, r_out, cp_out,
+                        block_complete=done, gate_is_log=use_log_a, r_is_log=log_space)
+    if dt != out_dt:
+        y_t, h_out = y_t.to(out_dt), h_out.to(out_dt)
+        cp_out = None if cp_out is None else cp_out.to(out_dt)
+    if gdt != gate_out_dt:
+        r_out = r_out.to(gate_out_dt)
+    return y_t, JagState(h_loc=h_out, r_pref=None if log_space else r_out,
+                         c_prev_loc=cp_out if done else state.c_prev_loc, i=0 if done else state.i + 1,
+                         block_len=state.block_len, use_log_r=log_space, log_r_pref=r_out if log_space else None)

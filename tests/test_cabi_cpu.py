@@ -107,6 +107,28 @@ def test_gated_entry_points_check_their_arguments(lib):
     assert bwd(ptrs=(16, 16, 16, 16, 16, 4, 16, 16, 16)) == -5
 
 
+def test_streaming_entry_points_check_their_arguments(lib):
+    p, ll = ctypes.c_void_p, ctypes.c_longlong
+
+    def step(ptrs=(16,) * 11, n=4, done=0, dtype=1, gdtype=1):
+        return lib.btp_sm100_decode_step(*[p(x) for x in ptrs], ll(n), done, 0, 0, dtype, gdtype, p(0))
+
+    def state(ptrs=(16,) * 5, n=4, L=20, dtype=0, gdtype=1):
+        return lib.btp_sm100_prefill_state(*[p(x) for x in ptrs], ll(n), L, 0, dtype, gdtype, p(0))
+
+    err = lambda: lib.btp_sm100_last_error().decode()
+    assert step(n=0) == -2
+    assert step(dtype=2) == -4 and step(gdtype=5) == -4
+    assert step(ptrs=(16, 0) + (16,) * 9) == -1
+    assert step(ptrs=(16,) * 10 + (0,), done=1) == -1 and "completes a block" in err()
+    assert step(ptrs=(16, 8) + (16,) * 9) == -5
+    assert step(ptrs=(2,) + (16,) * 10) == -5          # float gate on a 2-byte boundary
+    assert state(L=0) == -2 and state(n=-1) == -2
+    assert state(dtype=2) == -4
+    assert state(ptrs=(16, 16, 0, 16, 16)) == -1
+    assert state(ptrs=(2, 16, 16, 16, 16)) == -5
+
+
 def test_no_gpu_is_an_error_not_a_fallback(lib):
     """With valid arguments and no usable device the call fails with a CUDA error code; nothing is computed."""
     import torch
