@@ -1,6 +1,13 @@
-"""Timing of the gated (token-major) op and of the whole Phalanx layer on one GPU.
+"""Timing of the gated (token-major) op and of the whole Phalanx layer, on one GPU or batch-sharded over several.
 
     python -m spear_b200.bench_layer [--batch 1024 --length 128 --dim 512] [--steps 50] [--what gated|layer|both]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m spear_b200.bench_layer --what layer --batch 64 --length 2048 --dim 2048 --decay-mix
+
+Under torch.distributed.run `--batch` is the GLOBAL batch: each rank takes its slice (strong scaling, no
+exchange on the forward/backward data path), times are the maximum over ranks and rank 0 prints.  With
+`--allreduce-grads` each step also sums the parameter gradients over the ranks (one NCCL all-reduce of the
+flattened gradients), which is what data-parallel training adds to the layer.
 
 `gated`: one fused forward + one fused backward launch per step on resident inputs; reports time per
 launch and achieved GB/s against the algorithmic bytes (forward 130 B, backward 228 B per head-token:
@@ -13,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 
 import torch
 
@@ -65,23 +73,48 @@ def bench_gated(B, L, H, steps, sets):
     }
 
 
-def bench_layer(B, L, dim, steps):
-    from spear_b200.nn.phalanx import Phalanx
+def set_decay_mix(layer) -> None:
+    """Input-independent decays: half the heads get log a ~ U(-1e-3, 0), the other half U(-4, -1)."""
+    prm = layer.param
+    H = prm.proj_a.bias.numel()
+    g = torch.Generator().manual_seed(7)
+    log_a = torch.cat([torch.rand(H // 2, generator=g) * -1e-3, -1.0 - 3.0 * torch.rand(H - H // 2, generator=g)])
+    a = torch.exp(log_a.double()).clamp(max=1.0 - 1e-12)
+    with torch.no_grad():
+        prm.proj_a.weight.zero_()
+        prm.proj_a.bias.copy_(torch.log(a / (1.0 - a)).to(prm.proj_a.bias.dtype))  # sigmoid(bias) = a
 
-    torch.manual_seed(0)
+
+def bench_layer(B, L, dim, steps, *, decay_mix=False, allreduce_grads=False, rank=0, world=1):
+    from spear_b200.nn.phalanx import Phalanx
+    from spear_b200.sharding import batch_shard, max_over_ranks
+
+    torch.manual_seed(0)  # every rank holds the same weights
     layer = Phalanx(dim=dim, length=L, dtype=torch.bfloat16).cuda()
-    u = torch.randn(B, L, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    do = torch.randn(B, L, dim, device="cuda", dtype=torch.bfloat16)
+    if decay_mix:
+        set_decay_mix(layer)
+    lo, hi = batch_shard(B, rank, world)
+    torch.manual_seed(1 + rank)
+    u = torch.randn(hi - lo, L, dim, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    do = torch.randn(hi - lo, L, dim, device="cuda", dtype=torch.bfloat16)
+    params = list(layer.parameters())
 
     def step():
         layer.zero_grad(set_to_none=True)
         u.grad = None
         layer(u).backward(do)
+        if allreduce_grads and world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            torch.distributed.all_reduce(flat)
 
-    out = {"what": "phalanx_layer_fwd_bwd", "B": B, "L": L, "dim": dim}
+    out = {"what": "phalanx_layer_fwd_bwd", "global_batch": B, "L": L, "dim": dim, "n_gpus": world,
+           "batch_per_gpu": hi - lo, "decay_mix": bool(decay_mix), "allreduce_grads": bool(allreduce_grads and world > 1)}
     for fused in (True, False):
         layer.fused_gating = fused
+        if world > 1:
+            torch.distributed.barrier()
         t = _timed(step, steps, warm=2)
+        t = max_over_ranks([t], device="cuda")[0] if world > 1 else t
         out["fused_ms" if fused else "unfused_ms"] = t / 1e3
     out["tokens_per_s_fused"] = B * L / (out["fused_ms"] * 1e-3)
     out["speedup"] = out["unfused_ms"] / out["fused_ms"]
@@ -96,13 +129,26 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--sets", type=int, default=3)
     ap.add_argument("--what", default="both", choices=["gated", "layer", "both"])
+    ap.add_argument("--decay-mix", action="store_true", help="layer: fixed decays, half the heads near 1, half fast")
+    ap.add_argument("--allreduce-grads", action="store_true", help="layer, several ranks: sum parameter gradients each step")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
-    if args.what in ("gated", "both"):
-        print(json.dumps(bench_gated(args.batch, args.length, args.dim // 16, args.steps, args.sets)), flush=True)
-    if args.what in ("layer", "both"):
-        print(json.dumps(bench_layer(args.batch, args.length, args.dim, max(3, args.steps // 10))), flush=True)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    try:
+        if args.what in ("gated", "both") and rank == 0:
+            print(json.dumps(bench_gated(args.batch, args.length, args.dim // 16, args.steps, args.sets)), flush=True)
+        if args.what in ("layer", "both"):
+            res = bench_layer(args.batch, args.length, args.dim, max(3, args.steps // 10), decay_mix=args.decay_mix,
+                              allreduce_grads=args.allreduce_grads, rank=rank, world=world)
+            if rank == 0:
+                print(json.dumps(res), flush=True)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":
