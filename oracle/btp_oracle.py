@@ -197,3 +197,29 @@ def error_metrics(got: torch.Tensor, want: torch.Tensor, eps: float = 1e-7) -> d
         "rmse": ad.square().mean().sqrt().item(),
         "rel_l2": rel_l2(got, want),
     }
+
+
+def phalanx_forward(state: dict, u: torch.Tensor, k: int = 2, kv_heads: int | None = None) -> torch.Tensor:
+    """The Phalanx layer's data flow around the oracle op, in the dtype of `u` on CPU.
+
+    Follows spear/nn/phalanx/swr.py:157-175 (the four projections), :96-103 (head h reads key/value head
+    h // (heads / kv_heads)), :196-221 (A = sigmoid, X = sigmoid(B) * V), :311-327 (y * C + V, output
+    projection).  `state` is the layer's state_dict (same parameter names as the reference's).
+    """
+    lin = lambda name, t: torch.nn.functional.linear(t, state[f"param.{name}.weight"].to(t.dtype),
+                                                     None if f"param.{name}.bias" not in state
+                                                     else state[f"param.{name}.bias"].to(t.dtype))
+    Bsz, L, dim = u.shape
+    H = state["param.proj_a.weight"].shape[0]
+    D = state["param.proj_v.weight"].shape[0] // H
+    KV = H if kv_heads is None else kv_heads
+    idx = torch.arange(H) // (H // KV)
+    heads = lambda t, n: t.transpose(1, 2).reshape(Bsz, n, D, L)
+    A = torch.sigmoid(lin("proj_a", u)).transpose(1, 2)
+    Bg = heads(lin("proj_b", u), KV).index_select(1, idx)
+    C = heads(lin("proj_c", u), KV).index_select(1, idx)
+    V = heads(lin("proj_v", u), H)
+    X = torch.sigmoid(Bg) * V
+    y = btp_forward(A.contiguous(), X.contiguous(), k) * C + V
+    y = y.reshape(Bsz, H * D, L).transpose(1, 2)
+    return torch.nn.functional.linear(y, state["proj_out.weight"].to(u.dtype))

@@ -126,6 +126,45 @@ def make_layer_fixture(root: str):
         print(f"wrote {name}.npz")
 
 
+CFG0 = dict(dim=512, length=128, batch=8, weight_seed=2024, input_seed=4048, stride=8)
+
+
+def cfg0_inputs():
+    """Inputs of the `dim=512, length=128, batch=8, fp32` layer case, regenerated from seeds by the test."""
+    g = torch.Generator().manual_seed(CFG0["input_seed"])
+    u = torch.randn(CFG0["batch"], CFG0["length"], CFG0["dim"], generator=g)
+    dout = torch.randn(CFG0["batch"], CFG0["length"], CFG0["dim"], generator=g)
+    return u, dout
+
+
+def make_cfg0_fixture(root: str):
+    """The reference's own CPU-runnable configuration: Phalanx forward (and backward) in float32 through its
+    PyTorch path.  Weights and inputs come from seeds, so the fixture only keeps checksums of them (the test
+    refuses to run if its regenerated tensors differ) and a strided sample of the outputs with their norms."""
+    sys.path.insert(0, root)
+    sys.modules.setdefault("spear._btp", types.ModuleType("spear._btp"))
+    from spear.nn.phalanx import Phalanx  # noqa: WPS433
+
+    torch.manual_seed(CFG0["weight_seed"])
+    layer = Phalanx(dim=CFG0["dim"], length=CFG0["length"], method="pytorch", dtype=torch.float32)
+    layer.param.compute_dtype = torch.float32
+    u, dout = cfg0_inputs()
+    u_in = u.clone().requires_grad_(True)
+    out = layer(u_in)
+    out.backward(dout)
+    st = CFG0["stride"]
+    data = {"out_sample": out.detach()[:, ::st, ::st].numpy(), "du_sample": u_in.grad[:, ::st, ::st].numpy(),
+            "out_norm": np.array(out.detach().double().norm().item()), "du_norm": np.array(u_in.grad.double().norm().item()),
+            "u_checksum": np.array([u.double().sum().item(), u.double().abs().sum().item()]),
+            "dout_checksum": np.array([dout.double().sum().item(), dout.double().abs().sum().item()])}
+    for k, v in layer.state_dict().items():
+        data["wsum:" + k] = np.array([v.double().sum().item(), v.double().abs().sum().item()])
+    for k, p in layer.named_parameters():
+        data["gnorm:" + k] = np.array(p.grad.double().norm().item())
+    np.savez_compressed(os.path.join(HERE, "layer_cfg0.npz"), **data)
+    print("wrote layer_cfg0.npz")
+
+
 def make_inference_fixture(root: str):
     """Outputs of the reference's prefill + decode helpers (spear/nn/phalanx/inference.py), float32 on CPU."""
     sys.path.insert(0, root)
@@ -163,4 +202,5 @@ if __name__ == "__main__":
     torch.set_num_threads(4)
     make_op_fixtures(_load_reference_math(args.reference))
     make_layer_fixture(args.reference)
+    make_cfg0_fixture(args.reference)
     make_inference_fixture(args.reference)

@@ -350,6 +350,36 @@ def test_phalanx_layer_matches_reference_layer(native, case, kv_heads):
         assert m["rel_l2"] <= 6e-2, f"grad {name} rel_l2 {m['rel_l2']:.3e}"
 
 
+@pytest.mark.parametrize("fused", [True, False])
+def test_phalanx_layer_at_the_reference_cpu_configuration(native, fused):
+    """dim 512, length 128, batch 8: the configuration the reference runs on CPU in float32.  Here the same
+    weights and inputs (regenerated from seeds, verified by checksum) go through the bf16 layer on the kernels."""
+    from test_oracle import cfg0_tensors
+
+    from spear_b200.nn.phalanx import Phalanx
+
+    g, seeded, u, dout, st = cfg0_tensors()
+    layer = Phalanx(dim=u.shape[-1], length=u.shape[1], dtype=torch.bfloat16).cuda()
+    layer.load_state_dict({k: v.to(torch.bfloat16) for k, v in seeded.state_dict().items()})
+    layer.fused_gating = fused
+    ud = u.cuda().to(torch.bfloat16).requires_grad_(True)
+    out = layer(ud)
+    out.backward(dout.cuda().to(torch.bfloat16))
+    m = O.error_metrics(out.float().cpu()[:, ::st, ::st], g["out_sample"])
+    for key, lim in LAYER_FORWARD_LIMITS.items():
+        assert m[key] <= lim, f"layer out {key}={m[key]:.3e}"
+    assert m["rel_l2"] <= 3e-2, m
+    assert abs(out.double().norm().item() / g["out_norm"].item() - 1.0) <= 1e-2
+    m = O.error_metrics(ud.grad.float().cpu()[:, ::st, ::st], g["du_sample"])
+    for key, lim in LAYER_BACKWARD_LIMITS.items():
+        assert m[key] <= lim, f"layer du {key}={m[key]:.3e}"
+    assert m["rel_l2"] <= 5e-2, m
+    assert abs(ud.grad.double().norm().item() / g["du_norm"].item() - 1.0) <= 2e-2
+    for name, prm in layer.named_parameters():
+        ratio = prm.grad.double().norm().item() / g["gnorm:" + name].item()
+        assert abs(ratio - 1.0) <= 3e-2, f"|grad {name}| is {ratio:.4f} of the reference's"
+
+
 # ------------------------------------------------------------------ gated op in token-major layout (the layer's glue, fused)
 def _gated_oracle(a_logits, b_logits, c, v, k=2):
     """The layer's data flow in float32 on CPU around the oracle op; the decay is rounded to bf16 as the

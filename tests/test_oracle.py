@@ -3,6 +3,9 @@ PyTorch path (tests/golden/make_golden.py).  No GPU needed."""
 
 from __future__ import annotations
 
+import os
+import sys
+
 import pytest
 import torch
 
@@ -95,3 +98,38 @@ def test_shape_validation():
         O.btp_forward(a, x)
     with pytest.raises(ValueError):
         O.btp_forward(torch.rand(1, 3, 32), torch.rand(1, 2, 16, 32))
+
+
+# ------------------------------------------------------------------ the layer's data flow around the op
+@pytest.mark.parametrize("case,kv_heads", [("layer_basic", None), ("layer_kv2", 2)])
+def test_oracle_layer_matches_reference_layer(case, kv_heads):
+    g = load_golden(case)
+    state = {k[2:]: v for k, v in g.items() if k.startswith("w:")}
+    out = O.phalanx_forward(state, g["u"], kv_heads=kv_heads)
+    assert torch.allclose(out, g["out"], rtol=1e-4, atol=1e-5)
+
+
+def cfg0_tensors():
+    """Weights and inputs of the reference's CPU-runnable configuration (dim 512, length 128, batch 8, float32),
+    regenerated from the seeds tests/golden/make_golden.py used and verified against the stored checksums."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+    from make_golden import CFG0, cfg0_inputs
+    from spear_b200.nn.phalanx import Phalanx
+
+    g = load_golden("layer_cfg0")
+    torch.manual_seed(CFG0["weight_seed"])
+    layer = Phalanx(dim=CFG0["dim"], length=CFG0["length"], dtype=torch.float32)
+    u, dout = cfg0_inputs()
+    chk = lambda t: torch.tensor([t.double().sum().item(), t.double().abs().sum().item()], dtype=torch.float64)
+    for name, t in layer.state_dict().items():
+        assert torch.allclose(chk(t), g["wsum:" + name], rtol=1e-12, atol=0), f"seeded init of {name} differs from the fixture's"
+    assert torch.allclose(chk(u), g["u_checksum"], rtol=1e-12, atol=0)
+    assert torch.allclose(chk(dout), g["dout_checksum"], rtol=1e-12, atol=0)
+    return g, layer, u, dout, CFG0["stride"]
+
+
+def test_oracle_layer_matches_reference_at_its_cpu_configuration():
+    g, layer, u, _, st = cfg0_tensors()
+    out = O.phalanx_forward(layer.state_dict(), u)
+    assert torch.allclose(out[:, ::st, ::st], g["out_sample"], rtol=1e-4, atol=1e-5)
+    assert abs(out.double().norm().item() / g["out_norm"].item() - 1.0) < 1e-5
