@@ -120,20 +120,21 @@ def backward(coeff, x, dy, checkpoint, dx, dA, k: int, wpb: int, *, log_coeff: b
 
 
 def decode_step(a_t, x_t, c_t, v_t, y_t, h_loc, r_pref, c_prev_loc, h_loc_out, r_pref_out, c_prev_loc_out, *,
-                block_complete: bool, gate_is_log: bool, r_is_log: bool) -> None:
+                block_complete: bool, gate_is_log: bool, r_is_log: bool, _checked: bool = False) -> None:
     """One streaming step in one launch (btp_sm100_decode_step).  No counterpart in ``spear._btp``: the reference
     does this with tensor ops (spear/nn/phalanx/inference.py:177-266).  All tensors contiguous, [.., 16] ones of one
     dtype (bfloat16 or float32), a_t / r_pref / r_pref_out of one dtype (bfloat16 or float32)."""
-    big = (x_t, c_t, v_t, y_t, h_loc, c_prev_loc, h_loc_out) + (() if c_prev_loc_out is None else (c_prev_loc_out,))
-    small = (a_t, r_pref_out) + (() if r_pref is None else (r_pref,))
-    _require(all(t.is_cuda for t in big + small), "decode_step needs CUDA tensors (there is no CPU path)")
-    _require(x_t.dim() >= 1 and x_t.shape[-1] == DH, f"x_t must be [..., {DH}]")
-    _require(all(t.shape == x_t.shape and t.dtype == x_t.dtype and t.is_contiguous() for t in big),
-             "x_t, c_t, v_t, y_t and the [.,16] states must share shape and dtype and be contiguous")
-    _require(all(t.shape == x_t.shape[:-1] and t.dtype == a_t.dtype and t.is_contiguous() for t in small),
-             "a_t and the r_pref states must be [...] of one dtype and contiguous")
-    _require(x_t.dtype in _TAG and a_t.dtype in _TAG, "decode_step takes bfloat16 or float32 tensors")
-    _require(not block_complete or c_prev_loc_out is not None, "the step that completes a block writes c_prev_loc_out")
+    if not _checked:  # step_jagged builds every tensor itself and skips this
+        big = (x_t, c_t, v_t, y_t, h_loc, c_prev_loc, h_loc_out) + (() if c_prev_loc_out is None else (c_prev_loc_out,))
+        small = (a_t, r_pref_out) + (() if r_pref is None else (r_pref,))
+        _require(all(t.is_cuda for t in big + small), "decode_step needs CUDA tensors (there is no CPU path)")
+        _require(x_t.dim() >= 1 and x_t.shape[-1] == DH, f"x_t must be [..., {DH}]")
+        _require(all(t.shape == x_t.shape and t.dtype == x_t.dtype and t.is_contiguous() for t in big),
+                 "x_t, c_t, v_t, y_t and the [.,16] states must share shape and dtype and be contiguous")
+        _require(all(t.shape == x_t.shape[:-1] and t.dtype == a_t.dtype and t.is_contiguous() for t in small),
+                 "a_t and the r_pref states must be [...] of one dtype and contiguous")
+        _require(x_t.dtype in _TAG and a_t.dtype in _TAG, "decode_step takes bfloat16 or float32 tensors")
+        _require(not block_complete or c_prev_loc_out is not None, "the step that completes a block writes c_prev_loc_out")
     n_heads = a_t.numel()
     if n_heads == 0:
         return

@@ -52,12 +52,13 @@ def _kernel_dtype(*tensors):
     """Storage type the kernels run in: the promoted type if it is bfloat16 or float32, else float32."""
     dt = tensors[0].dtype
     for t in tensors[1:]:
-        dt = torch.promote_types(dt, t.dtype)
+        if t.dtype != dt:
+            dt = torch.promote_types(dt, t.dtype)
     return dt, (dt if dt in _KERNEL_DTYPES else torch.float32)
 
 
 def _as(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
-    return t.to(dtype).contiguous()
+    return t if (t.dtype == dtype and t.is_contiguous()) else t.to(dtype).contiguous()
 
 
 @torch.no_grad()
@@ -108,8 +109,11 @@ def step_jagged(A_t, X_t, C_t, V_t, state: JagState, *, use_log_a: bool = False)
     `c_prev_loc` is shared between consecutive states until a block completes.  Arithmetic is fp32 with a single
     rounding to the storage type, where the reference rounds after every tensor op.
     """
-    if not (A_t.is_cuda and X_t.is_cuda):
+    if not (A_t.is_cuda and X_t.is_cuda and state.h_loc.is_cuda):
         raise RuntimeError("step_jagged needs CUDA tensors: this package has no CPU path")
+    if X_t.shape[-1] != 16 or A_t.shape != X_t.shape[:-1] or not (
+            C_t.shape == V_t.shape == X_t.shape == state.h_loc.shape == state.c_prev_loc.shape):
+        raise ValueError("step_jagged takes A_t [B,H] and X_t, C_t, V_t, state.h_loc, state.c_prev_loc [B,H,16]")
     if state.block_len != BLOCK:
         raise NotImplementedError(f"the kernel's block length is {BLOCK} (got block_len={state.block_len})")
     log_space = bool(state.use_log_r or use_log_a)
@@ -120,12 +124,14 @@ def step_jagged(A_t, X_t, C_t, V_t, state: JagState, *, use_log_a: bool = False)
     h_in, cp_in = _as(state.h_loc, dt), _as(state.c_prev_loc, dt)
     r_in = None if r_prev is None else _as(r_prev, gdt)
     done = state.i + 1 == state.block_len
-    y_t = torch.empty_like(x_t)
-    h_out = torch.empty_like(x_t)
+    if r_in is not None and r_in.shape != a_t.shape:
+        raise ValueError("the state's gate product must have the shape of A_t")
+    buf = torch.empty((3 if done else 2,) + x_t.shape, device=x_t.device, dtype=dt)  # one allocation
+    y_t, h_out = buf[0], buf[1]
+    cp_out = buf[2] if done else None
     r_out = torch.empty_like(a_t)
-    cp_out = torch.empty_like(x_t) if done else None
     _native.decode_step(a_t, x_t, c_t, v_t, y_t, h_in, r_in, cp_in, h_out, r_out, cp_out,
-                        block_complete=done, gate_is_log=use_log_a, r_is_log=log_space)
+                        block_complete=done, gate_is_log=use_log_a, r_is_log=log_space, _checked=True)
     if dt != out_dt:
         y_t, h_out = y_t.to(out_dt), h_out.to(out_dt)
         cp_out = None if cp_out is None else cp_out.to(out_dt)
