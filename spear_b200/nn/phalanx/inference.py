@@ -78,16 +78,23 @@ def parallel_jagged(A, X, C, V, *, block_len: int, use_log_a: bool = False):
     if L < 1:
         raise ValueError("the prompt must hold at least one token")
     pad = (-L) % BLOCK
-    coeff = A.float()
-    x = X.to(torch.bfloat16)
+    # The kernel takes bf16 x and bf16 / float32 gates (float32 log gates); tensors already in that form are
+    # passed as they are, without a copy.
+    coeff = A.float() if (use_log_a or A.dtype not in _KERNEL_DTYPES) else A
+    x = X if X.dtype == torch.bfloat16 else X.to(torch.bfloat16)
     if pad:
         coeff = torch.nn.functional.pad(coeff, (0, pad), value=0.0 if use_log_a else 1.0)
         x = torch.nn.functional.pad(x, (0, pad), value=0.0)
     coeff = coeff.contiguous()
     x = x.contiguous()
-    y = torch.empty(x.shape, device=x.device, dtype=torch.float32)
+    low = V.dtype == torch.bfloat16 and C.dtype == torch.bfloat16
+    y = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16 if low else torch.float32)
     _native.forward(coeff, x, y, None, 2, 32, log_coeff=use_log_a)
-    Y = (y[..., :L] * C.float() + V.float()).to(V.dtype)
+    y = y[..., :L] if pad else y
+    if low:
+        Y = torch.addcmul(V, y, C)  # one pass, fp32 arithmetic inside, one rounding
+    else:
+        Y = torch.addcmul(V.float(), y, C.float()).to(V.dtype)
 
     # hand-off state (inference.py:333-358): one launch over the last partial block and the complete one before it
     _, xdt = _kernel_dtype(X)
