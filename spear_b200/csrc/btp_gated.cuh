@@ -80,7 +80,7 @@ __device__ __forceinline__ void gated_halo_left(const GatedParams& p, long long 
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int tok = 2 * t + (j & 1) + ((j >> 1) << 3);
-    const float w = round_bf16(ex2(T15 - __shfl_sync(0xffffffffu, T, tok)));
+    const float w = lmat_weight<true>(ex2(T15 - __shfl_sync(0xffffffffu, T, tok)));
     const long long rb = (row0 + tok) * p.ld_b + h * 16;
     const long long rv = (row0 + tok) * p.ld_v + h * 16;
     const float x_g = gate_scalar(__bfloat162float(p.b_logits[rb + g]), __bfloat162float(p.v[rv + g]));

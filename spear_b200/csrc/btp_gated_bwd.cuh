@@ -59,7 +59,7 @@ __device__ __forceinline__ void gated_halo_right(const GatedBwdParams& p, long l
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int tok = 2 * t + (j & 1) + ((j >> 1) << 3);
-    const float w = round_bf16(ex2(__shfl_sync(0xffffffffu, T, tok) - T0));
+    const float w = lmat_weight<true>(ex2(__shfl_sync(0xffffffffu, T, tok) - T0));
     const long long rd = (row0 + tok) * p.ld_do + h * 16;
     const long long rc = (row0 + tok) * p.ld_c + h * 16;
     const float dy_g = round_bf16(__bfloat162float(p.dout[rd + g]) * __bfloat162float(p.c[rc + g]));

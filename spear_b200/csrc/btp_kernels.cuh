@@ -278,11 +278,12 @@ __device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int l
 
 // Halo: a 16x16 block that belongs to a neighbouring warp's range is read straight from global
 // memory and reduced to the 16 numbers the seam needs.
-//   LEFT  (RIGHT == false): carry  = sum_c  x[ch,c] * bf16(2^(T_15 - T_c))             (= v[:,15])
-//   RIGHT (RIGHT == true) : dCarry = 2^(T_0) * sum_r dy[ch,r] * bf16(2^(T_r - T_0))
-// The weights are rounded to bf16 exactly like the Lmat operand of the tensor-core path.
+//   LEFT  (RIGHT == false): carry  = sum_c  x[ch,c] * w(2^(T_15 - T_c))             (= v[:,15])
+//   RIGHT (RIGHT == true) : dCarry = 2^(T_0) * sum_r dy[ch,r] * w(2^(T_r - T_0))
+// w() represents a weight exactly like the Lmat operand of the tensor-core path: one bf16 term, or two
+// (hi + lo) when PRECISE.
 // Returns the values for channels g and g+8 (g = lane >> 2), identical in the 4 lanes of a group.
-template <int COEF, bool TILE_F32, bool RIGHT>
+template <int COEF, bool TILE_F32, bool RIGHT, bool PRECISE>
 __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* coeff_base, int L, long long bh,
                                             int tok0, int lane, float& out_g, float& out_g8) {
   const int g = lane >> 2, t = lane & 3;
@@ -304,7 +305,7 @@ __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* c
   for (int j = 0; j < 4; ++j) {
     const int tok = 2 * t + (j & 1) + ((j >> 1) << 3);
     const float Tj = __shfl_sync(0xffffffffu, T, tok);
-    w[j] = round_bf16(ex2(RIGHT ? (Tj - Tref) : (Tref - Tj)));
+    w[j] = lmat_weight<PRECISE>(ex2(RIGHT ? (Tj - Tref) : (Tref - Tj)));
   }
   float e[2][4];  // [row half][token]
   const long long row_g = (bh * 16 + g) * static_cast<long long>(L) + tok0;
@@ -520,7 +521,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
     } else if (j == 0) {
-      halo_reduce<COEF, false, false>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
+      halo_reduce<COEF, false, false, PRECISE>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
     }
 
     const float* tg = tab + tl.g;
@@ -852,7 +853,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     float* tab = ws.tab_ptr(tset);
     chunk_tables<COEF, TL, true>(ws.raw_ptr(s), tab, lane, carry_scale);
     if (j == 0 && cons.cs != 0 && p.use_carry) {
-      halo_reduce<COEF, false, false>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
+      halo_reduce<COEF, false, false, PRECISE>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
     }
     const float* tg = tab + tl.g;
     const float* tt = tab + 2 * tl.t;
@@ -911,7 +912,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     float dc_g = 0.0f, dc_g8 = 0.0f;
     if (!p_seq_end && p.use_carry) {
       // the block to the right belongs to another warp: recompute what it sends
-      halo_reduce<COEF, DY_F32, true>(p.dy, p.coeff, L, p_bh, p_c0 + 16 * p_nt, lane, dc_g, dc_g8);
+      halo_reduce<COEF, DY_F32, true, PRECISE>(p.dy, p.coeff, L, p_bh, p_c0 + 16 * p_nt, lane, dc_g, dc_g8);
     }
     back(accB, p_tt, p_da, p_o0, p_cg, p_cg8, dc_g, dc_g8);
     flush();

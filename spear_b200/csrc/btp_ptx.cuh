@@ -202,6 +202,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 __device__ __forceinline__ float round_bf16(float v) { return bf16_lo(pack_bf16x2(v, 0.0f)); }
+// Value that the tensor-core path effectively multiplies by when an Lmat entry `v` is fed as one bf16 term
+// (SPLIT == false) or as two (hi + lo, SPLIT == true); the scalar halo code uses it so that a result does
+// not depend on where the seams between warps fall.
+template <bool SPLIT>
+__device__ __forceinline__ float lmat_weight(float v) {
+  const float hi = round_bf16(v);
+  if constexpr (SPLIT) {
+    return hi + round_bf16(v - hi);
+  } else {
+    return hi;
+  }
+}
 
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");

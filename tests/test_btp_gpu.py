@@ -143,6 +143,18 @@ def test_backward_vs_oracle(native, B, H, L, seed, cstd):
         assert_limits(dA, dA_w, BACKWARD_LIMITS, f"dA dy={dy_dtype}")
 
 
+@pytest.mark.parametrize("B,H,L", [(1, 2, 4096), (2, 8, 512), (64, 32, 128)])
+def test_dA_keeps_float32_accuracy_with_and_without_seams(native, B, H, L):
+    """The Lmat operand is fed as two bf16 terms, which leaves dA at float32 accuracy.  Few long sequences are
+    cut into per-warp ranges whose seams are recomputed by scalar code: those blocks must be as accurate as
+    the ones in the middle of a range (the scalar code uses the same two-term weights)."""
+    a, x, dy = sample(B, H, L, 17, 1.0)
+    dA_w, _ = O.btp_backward(a.double(), x.double(), dy.double())
+    dA, _ = run_bwd(native, a, x, dy)
+    rel = O.rel_l2(dA.double(), dA_w)
+    assert rel <= 5e-6, f"dA rel_l2 {rel:.3e}"
+
+
 def test_float32_and_log_coefficients(native):
     """Superset entry: coefficients that bf16 cannot hold (log a ~ U(-1e-3, 0))."""
     g = torch.Generator().manual_seed(11)
