@@ -67,56 +67,81 @@ def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
 
 
 def _check_common(coeff: torch.Tensor, x: torch.Tensor, k: int, wpb: int) -> tuple[int, int, int]:
-    _require(x.is_cuda and coeff.is_cuda, "BTP tensors must be CUDA tensors (there is no CPU path)")
-    _require(x.dim() == 4 and x.shape[2] == DH, f"x must be [B, H, {DH}, L], got {tuple(x.shape)}")
+    # plain `if`s: the messages are only formatted when a check fails (this runs on every call)
+    if not (x.is_cuda and coeff.is_cuda):
+        raise RuntimeError("BTP tensors must be CUDA tensors (there is no CPU path)")
+    if x.dim() != 4 or x.shape[2] != DH:
+        raise RuntimeError(f"x must be [B, H, {DH}, L], got {tuple(x.shape)}")
     B, H, _, L = x.shape
-    _require(tuple(coeff.shape) == (B, H, L), f"coeff must be [B, H, L] = {(B, H, L)}, got {tuple(coeff.shape)}")
-    _require(L % BLK == 0, f"Length L must be multiple of {BLK}")
-    _require(k in (1, 2), "k must be 1 or 2")
-    _require(wpb in SUPPORTED_WPB, f"WPB must be one of {list(SUPPORTED_WPB)}")
-    _require(x.dtype == torch.bfloat16, f"x must be bfloat16 (got {x.dtype}); this build is bf16-only")
-    _require(coeff.dtype in (torch.bfloat16, torch.float32), f"coeff must be bfloat16 or float32 (got {coeff.dtype})")
-    _require(x.is_contiguous() and coeff.is_contiguous(), "coeff and x must be contiguous")
-    _require(coeff.device == x.device, "coeff and x must be on the same device")
+    if coeff.shape != (B, H, L):
+        raise RuntimeError(f"coeff must be [B, H, L] = {(B, H, L)}, got {tuple(coeff.shape)}")
+    if L % BLK != 0:
+        raise RuntimeError(f"Length L must be multiple of {BLK}")
+    if k != 1 and k != 2:
+        raise RuntimeError("k must be 1 or 2")
+    if wpb not in SUPPORTED_WPB:
+        raise RuntimeError(f"WPB must be one of {list(SUPPORTED_WPB)}")
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError(f"x must be bfloat16 (got {x.dtype}); this build is bf16-only")
+    if coeff.dtype != torch.bfloat16 and coeff.dtype != torch.float32:
+        raise RuntimeError(f"coeff must be bfloat16 or float32 (got {coeff.dtype})")
+    if not (x.is_contiguous() and coeff.is_contiguous()):
+        raise RuntimeError("coeff and x must be contiguous")
+    if coeff.device != x.device:
+        raise RuntimeError("coeff and x must be on the same device")
     return B, H, L
 
 
 def forward(coeff, x, y, checkpoint, k: int, wpb: int, *, log_coeff: bool = False) -> None:
     """y <- btp(coeff, x); optionally fills the reference's carry checkpoint."""
     B, H, L = _check_common(coeff, x, k, wpb)
-    _require(y.shape == x.shape and y.is_contiguous() and y.device == x.device, "y must match x and be contiguous")
-    _require(y.dtype in _TAG, f"y must be bfloat16 or float32 (got {y.dtype})")
+    if y.shape != x.shape or not y.is_contiguous() or y.device != x.device:
+        raise RuntimeError("y must match x and be contiguous")
+    ytag = _TAG.get(y.dtype)
+    if ytag is None:
+        raise RuntimeError(f"y must be bfloat16 or float32 (got {y.dtype})")
     if checkpoint is not None and checkpoint.numel():
-        _require(checkpoint.dtype == torch.float32 and checkpoint.is_contiguous(), "checkpoint must be contiguous float32")
-        _require(tuple(checkpoint.shape) == (B, H, L // BLK, DH), "checkpoint must be [B, H, L/16, 16]")
+        if checkpoint.dtype != torch.float32 or not checkpoint.is_contiguous():
+            raise RuntimeError("checkpoint must be contiguous float32")
+        if checkpoint.shape != (B, H, L // BLK, DH):
+            raise RuntimeError("checkpoint must be [B, H, L/16, 16]")
+    if log_coeff and coeff.dtype != torch.float32:
+        raise RuntimeError("log-space coefficients must be float32")
     ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
-    _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
     if x.numel() == 0:  # nothing to compute (empty batch, no heads or no tokens)
         return
     with _OnDevice(x.device.index) as stream:
         rc = _lib.load().btp_sm100_forward(
-            _ptr(coeff), _ptr(x), _ptr(y), _ptr(checkpoint), B, H, L, int(k), ctag, _TAG[y.dtype], ctypes.c_void_p(stream)
+            _ptr(coeff), _ptr(x), _ptr(y), _ptr(checkpoint), B, H, L, int(k), ctag, ytag, ctypes.c_void_p(stream)
         )
-    _lib.check(rc, "btp_sm100_forward")
+    if rc:
+        _lib.check(rc, "btp_sm100_forward")
 
 
 def backward(coeff, x, dy, checkpoint, dx, dA, k: int, wpb: int, *, log_coeff: bool = False) -> None:
     """dx, dA <- gradients for upstream dy.  `checkpoint` is accepted and ignored."""
     B, H, L = _check_common(coeff, x, k, wpb)
-    _require(dy.shape == x.shape and dy.is_contiguous() and dy.device == x.device, "dy must match x and be contiguous")
-    _require(dy.dtype in _TAG, f"dy must be bfloat16 or float32 (got {dy.dtype})")
-    _require(dx.shape == x.shape and dx.dtype == x.dtype and dx.is_contiguous(), "dx must match x (shape, dtype)")
-    _require(tuple(dA.shape) == (B, H, L) and dA.dtype == torch.float32 and dA.is_contiguous(), "dA must be float32 [B, H, L]")
+    if dy.shape != x.shape or not dy.is_contiguous() or dy.device != x.device:
+        raise RuntimeError("dy must match x and be contiguous")
+    dytag = _TAG.get(dy.dtype)
+    if dytag is None:
+        raise RuntimeError(f"dy must be bfloat16 or float32 (got {dy.dtype})")
+    if dx.shape != x.shape or dx.dtype != x.dtype or not dx.is_contiguous():
+        raise RuntimeError("dx must match x (shape, dtype)")
+    if dA.shape != (B, H, L) or dA.dtype != torch.float32 or not dA.is_contiguous():
+        raise RuntimeError("dA must be float32 [B, H, L]")
+    if log_coeff and coeff.dtype != torch.float32:
+        raise RuntimeError("log-space coefficients must be float32")
     ctag = _lib.DTYPE_F32_LOG if log_coeff else _TAG[coeff.dtype]
-    _require(not log_coeff or coeff.dtype == torch.float32, "log-space coefficients must be float32")
     if x.numel() == 0:
         return
     with _OnDevice(x.device.index) as stream:
         rc = _lib.load().btp_sm100_backward(
-            _ptr(coeff), _ptr(x), _ptr(dy), _ptr(None), _ptr(dx), _ptr(dA), B, H, L, int(k), ctag, _TAG[dy.dtype],
+            _ptr(coeff), _ptr(x), _ptr(dy), _ptr(None), _ptr(dx), _ptr(dA), B, H, L, int(k), ctag, dytag,
             ctypes.c_void_p(stream),
         )
-    _lib.check(rc, "btp_sm100_backward")
+    if rc:
+        _lib.check(rc, "btp_sm100_backward")
 
 
 def decode_step(a_t, x_t, c_t, v_t, y_t, h_loc, r_pref, c_prev_loc, h_loc_out, r_pref_out, c_prev_loc_out, *,
