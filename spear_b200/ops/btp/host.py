@@ -65,21 +65,25 @@ def btp_fwd_bwd_host(coeff, x, dy, y, dx, dA, *, k: int = 2, slices: int = 8, de
         if lo >= hi:
             break
         n, r = hi - lo, i % depth
-        up, done = torch.cuda.Event(), torch.cuda.Event()
+        up_x, up_dy, fwd_done, done = (torch.cuda.Event() for _ in range(4))
         with torch.cuda.stream(s_in):
             s_in.wait_event(ring.free[r])  # the previous occupant of these buffers has been downloaded
             ring.a[r][:n].copy_(coeff[lo:hi], non_blocking=True)
             ring.x[r][:n].copy_(x[lo:hi], non_blocking=True)
+            up_x.record(s_in)              # forward can start while dy is still on its way
             ring.dy[r][:n].copy_(dy[lo:hi], non_blocking=True)
-            up.record(s_in)
+            up_dy.record(s_in)
         with torch.cuda.stream(s_run):
-            s_run.wait_event(up)
+            s_run.wait_event(up_x)
             _native.forward(ring.a[r][:n], ring.x[r][:n], ring.y[r][:n], None, k, 32)
+            fwd_done.record(s_run)
+            s_run.wait_event(up_dy)
             _native.backward(ring.a[r][:n], ring.x[r][:n], ring.dy[r][:n], None, ring.dx[r][:n], ring.dA[r][:n], k, 32)
             done.record(s_run)
         with torch.cuda.stream(s_out):
-            s_out.wait_event(done)
+            s_out.wait_event(fwd_done)     # y leaves while backward runs
             y[lo:hi].copy_(ring.y[r][:n], non_blocking=True)
+            s_out.wait_event(done)
             dx[lo:hi].copy_(ring.dx[r][:n], non_blocking=True)
             dA[lo:hi].copy_(ring.dA[r][:n], non_blocking=True)
             ring.free[r].record(s_out)
