@@ -181,10 +181,17 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
 
   constexpr int AHEAD = STAGES - 2;
   for (int k = 0; k < AHEAD && k < n; ++k) issue();
-  GatedCursor peek = cons;  // runs one unit ahead of the consumer for the logit prefetch
-  float zn[TPL];
+  // the logits run two units ahead of the consumer: a short chunk does not hide a global load
+  GatedCursor peek = cons;
+  float zn[TPL], zn2[TPL];
   load_logits(peek, zn);
   peek.next(ncs, hgs);
+#pragma unroll
+  for (int q = 0; q < TPL; ++q) zn2[q] = 0.0f;
+  if (n > 1) {
+    load_logits(peek, zn2);
+    peek.next(ncs, hgs);
+  }
 
   // lane-constant addressing of this warp's [16 tokens][16 channels] block inside a box (see the header)
   const uint32_t frag_off = ((lane & 7) + 8 * (lane >> 4)) * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
@@ -200,9 +207,12 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
     }
     float l2[TPL];
 #pragma unroll
-    for (int q = 0; q < TPL; ++q) l2[q] = logit_to_log2a(zn[q]);
-    if (j + 1 < n) {
-      load_logits(peek, zn);
+    for (int q = 0; q < TPL; ++q) {
+      l2[q] = logit_to_log2a(zn[q]);
+      zn[q] = zn2[q];
+    }
+    if (j + 2 < n) {
+      load_logits(peek, zn2);
       peek.next(ncs, hgs);
     }
     const bool ok = mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);

@@ -147,9 +147,14 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
     return (tok < L) ? __bfloat162float(p.a_logits[row * p.ld_a + c.hg * 4 + warp]) : 0.0f;
   };
   while (issued < STAGES - 1 && issued < n) issue();
+  // the logits run two chunks ahead of the consumer: a 32-token chunk is too short to hide a global load
   GatedCursor peek = cons;
-  float z_next = load_logit(peek);
+  float z_next = load_logit(peek), z_after = 0.0f;
   peek.next(ncs, hgs);
+  if (n > 1) {
+    z_after = load_logit(peek);
+    peek.next(ncs, hgs);
+  }
 
   const uint32_t frag_off = ((lane & 7) + 8 * (lane >> 4)) * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
 
@@ -304,8 +309,9 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
   uint32_t phase = 0;
   for (; j < n; ++j) {
     const float z = z_next;
-    if (j + 1 < n) {
-      z_next = load_logit(peek);
+    z_next = z_after;
+    if (j + 2 < n) {
+      z_after = load_logit(peek);
       peek.next(ncs, hgs);
     }
     const bool ok = mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);
