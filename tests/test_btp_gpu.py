@@ -155,6 +155,34 @@ def test_dA_keeps_float32_accuracy_with_and_without_seams(native, B, H, L):
     assert rel <= 5e-6, f"dA rel_l2 {rel:.3e}"
 
 
+def _random_cases(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g).item())
+    return [(r(1, 5), r(1, 9), 16 * r(1, 40), r(1, 2), r(0, 2), r(0, 1), 1000 + i) for i in range(n)]
+
+
+@pytest.mark.parametrize("B,H,L,k,coeff_kind,f32_io,seed", _random_cases(24, 99))
+def test_random_shapes_and_modes_vs_oracle(native, B, H, L, k, coeff_kind, f32_io, seed):
+    """Seeded sweep over small odd shapes crossed with k, coefficient form (bf16, float32, float32 log) and
+    float32 y / dy: every combination goes through its own template instance and the ragged-chunk code."""
+    a, x, dy = sample(B, H, L, seed, 1.5)
+    if coeff_kind:  # float32 coefficients that bf16 cannot hold
+        a = torch.sigmoid(torch.randn(B, H, L, generator=torch.Generator().manual_seed(seed)) * 1.5)
+    coeff = torch.log(a) if coeff_kind == 2 else a
+    kw = dict(k=k, coeff_dtype=torch.float32 if coeff_kind else torch.bfloat16, log_coeff=coeff_kind == 2)
+    io = torch.float32 if f32_io else torch.bfloat16
+    y_w = O.btp_forward(a, x, k)
+    dA_w, dx_w = O.btp_backward(a, x, dy, k)
+    if coeff_kind == 2:
+        dA_w = dA_w * a  # gradient with respect to log a
+    y = run_fwd(native, coeff, x, out_dtype=io, **kw)
+    dA, dx = run_bwd(native, coeff, x, dy, dy_dtype=io, **kw)
+    assert torch.isfinite(y).all() and torch.isfinite(dA).all() and torch.isfinite(dx).all()
+    assert_limits(y, y_w, FORWARD_LIMITS, "y")
+    assert_limits(dx, dx_w, BACKWARD_LIMITS, "dx")
+    assert_limits(dA, dA_w, BACKWARD_LIMITS, "dA")
+
+
 def test_float32_and_log_coefficients(native):
     """Superset entry: coefficients that bf16 cannot hold (log a ~ U(-1e-3, 0))."""
     g = torch.Generator().manual_seed(11)
