@@ -169,7 +169,19 @@ class Phalanx(nn.Module):
 
         u = x.to(self.compute_dtype)
         prm = self.param
-        if self.fused_projection and self.heads % 8 == 0:
+        if self.kv_heads < self.heads:
+            # Heads share key/value heads (KVRepeat, swr.py:96-103: head h reads key/value head h // group): the
+            # two shared tensors are repeated to all heads in one copy each, and autograd sums their gradients
+            # over the group; everything else stays fused.
+            batch, length, _ = u.shape
+            group = self.heads // self.kv_heads
+
+            def repeat(t):
+                t = t.view(batch, length, self.kv_heads, 1, self.head_dim)
+                return t.expand(batch, length, self.kv_heads, group, self.head_dim).reshape(batch, length, self.dim)
+
+            y = gated_btp(prm.proj_a(u), repeat(prm.proj_b(u)), repeat(prm.proj_c(u)), prm.proj_v(u), self.k)
+        elif self.fused_projection and self.heads % 8 == 0:
             weight = torch.cat([prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight], dim=0)
             bias = torch.cat([prm.proj_b.bias, prm.proj_c.bias, torch.zeros_like(prm.proj_b.bias), prm.proj_a.bias])
             y = gated_btp_wide(nn.functional.linear(u, weight, bias), self.heads, self.k)

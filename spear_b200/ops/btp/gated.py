@@ -21,8 +21,9 @@ __all__ = ["gated_btp", "gated_btp_wide", "gated_btp_supported"]
 
 
 def gated_btp_supported(heads: int, kv_heads: int, length: int) -> bool:
-    """The fused kernels take 4 heads per CTA and one key/value head per head."""
-    return heads % 4 == 0 and kv_heads == heads and length % 16 == 0
+    """The fused kernels take 4 heads per CTA and per-head B_logits and C; a layer whose heads share key/value
+    heads (kv_heads < heads) repeats those two tensors to all heads first (see Phalanx._forward_fused)."""
+    return heads % 4 == 0 and heads % kv_heads == 0 and length % 16 == 0
 
 
 def _rows(t: torch.Tensor, cols: int, what: str) -> int:

@@ -529,6 +529,36 @@ def test_fused_projection_matches_separate_projections(native):
         assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
 
 
+@pytest.mark.parametrize("kv_heads", [8, 2])
+def test_shared_key_value_heads_run_fused(native, kv_heads):
+    """kv_heads < heads: the layer repeats B_logits and C to all heads and stays on the gated kernels.  Checked
+    against the float32 oracle of the reference's data flow (head h reads key/value head h // group) and against
+    the operation-by-operation path, gradients included."""
+    from spear_b200 import _lib
+    from spear_b200.nn.phalanx import Phalanx
+
+    torch.manual_seed(15)
+    layer = Phalanx(dim=256, length=96, dtype=torch.bfloat16, kv_heads=kv_heads).cuda()  # 16 heads
+    g = torch.Generator().manual_seed(16)
+    u = torch.randn(3, 96, 256, generator=g)
+    dout = torch.randn(3, 96, 256, generator=g).bfloat16().cuda()
+    want = O.phalanx_forward({k: v.float().cpu() for k, v in layer.state_dict().items()}, u.bfloat16().float(), kv_heads=kv_heads)
+    res = {}
+    for fused in (True, False):
+        layer.fused_gating = fused
+        layer.zero_grad()
+        ui = u.cuda().requires_grad_(True)
+        n0 = _lib.launch_count()
+        out = layer(ui)
+        out.backward(dout)
+        assert _lib.launch_count() - n0 == 2  # one forward and one backward kernel either way
+        res[fused] = (out.detach().float().cpu(), ui.grad.float().cpu(), {n: p.grad.float().cpu() for n, p in layer.named_parameters()})
+        assert O.rel_l2(res[fused][0], want) <= 2e-2
+    assert O.rel_l2(res[True][1], res[False][1]) <= 2e-2
+    for name in res[True][2]:
+        assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
+
+
 def test_forward_backward_replay_from_a_cuda_graph(native):
     """The calls only enqueue work on the given stream (descriptors travel by value), so a captured
     forward+backward replays on new data in the same buffers."""
