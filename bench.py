@@ -147,8 +147,8 @@ def run_reference_arm(args, rank):
     # size the per-step sample so that the whole run stays within about two minutes
     probe = min(cpu_reference_tokens_per_s(8, 1, 1))
     per_seq = probe / 8
-    budget = 120.0 / max(1, args.steps + args.warmup)
-    batch = int(max(1, min(B, budget / per_seq)))
+    seconds_per_step = 120.0 / max(1, args.steps + args.warmup)
+    batch = int(max(1, min(B, seconds_per_step / per_seq)))
     times = cpu_reference_tokens_per_s(batch, args.steps, args.warmup)
     threads = torch.get_num_threads()
     total = sum(times)
