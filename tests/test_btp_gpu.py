@@ -559,6 +559,47 @@ def test_shared_key_value_heads_run_fused(native, kv_heads):
         assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
 
 
+def test_concurrent_calls_from_several_threads(native):
+    """The C ABI is re-entrant: four host threads, each on its own stream and with its own tensors, call forward
+    and backward at the same time (ctypes drops the GIL for the duration of a call) and get the results of a
+    single-threaded run, bit for bit.  A failing call in one thread does not disturb the others' error text."""
+    import threading
+
+    cases = [sample(3 + i, 4, 16 * (5 + 3 * i), 200 + i, 1.0) for i in range(4)]
+    want = []
+    for a, x, dy in cases:
+        y = run_fwd(native, a, x)
+        dA, dx = run_bwd(native, a, x, dy)
+        want.append((y, dA, dx))
+    got = [None] * 4
+    errors = []
+
+    def work(i):
+        try:
+            a, x, dy = cases[i]
+            with torch.cuda.stream(torch.cuda.Stream()):
+                for _ in range(20):
+                    y = run_fwd(native, a, x)
+                    dA, dx = run_bwd(native, a, x, dy)
+                    if i == 3:  # this thread also makes calls that fail
+                        with pytest.raises(RuntimeError, match="multiple of 16"):
+                            native.forward(dev(a[..., :8], torch.bfloat16), dev(x[..., :8], torch.bfloat16),
+                                           torch.empty(x.shape[:3] + (8,), device="cuda", dtype=torch.bfloat16), None, 2, 32)
+                got[i] = (y, dA, dx)
+        except BaseException as e:  # noqa: BLE001 - reported by the main thread
+            errors.append((i, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i in range(4):
+        for g, w, name in zip(got[i], want[i], ("y", "dA", "dx")):
+            assert torch.equal(g, w), f"thread {i}: {name} differs from the single-threaded run"
+
+
 def test_forward_backward_replay_from_a_cuda_graph(native):
     """The calls only enqueue work on the given stream (descriptors travel by value), so a captured
     forward+backward replays on new data in the same buffers."""
