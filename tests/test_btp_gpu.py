@@ -155,6 +155,31 @@ def test_dA_keeps_float32_accuracy_with_and_without_seams(native, B, H, L):
     assert rel <= 5e-6, f"dA rel_l2 {rel:.3e}"
 
 
+def test_layer_parametrised_inputs_at_the_length_the_reference_kernel_fails(native):
+    """B=1, H=16, L=8192 with A and X produced by the layer's own projections (dim 256, layer seed 987, input
+    seed 789): the case the reference documents as failing for its CUDA backward, grad_coeff max_abs about 11
+    against a limit of 0.5 (tests/btp/test_numerics.py:169-207).  Here it has to pass the same limits."""
+    from spear_b200.nn.phalanx import Phalanx
+
+    B, H, L, dim = 1, 16, 8192, 256
+    torch.manual_seed(987)
+    layer = Phalanx(dim=dim, length=L, dtype=torch.bfloat16).cuda()
+    g = torch.Generator(device="cuda").manual_seed(789)
+    u = torch.randn(B, L, dim, device="cuda", generator=g).bfloat16()
+    with torch.no_grad():
+        A, X, _, _ = layer.param.forward_axcv(u)
+    a, x = A.float().cpu().contiguous(), X.float().cpu().contiguous()
+    dy = torch.randn(B, H, 16, L, generator=torch.Generator().manual_seed(790)).bfloat16().float()
+    y_w = O.btp_forward(a.double(), x.double())
+    dA_w, dx_w = O.btp_backward(a.double(), x.double(), dy.double())
+    y = run_fwd(native, a, x)
+    dA, dx = run_bwd(native, a, x, dy)
+    for got, want_, limits, what in ((y, y_w, FORWARD_LIMITS, "y"), (dx, dx_w, BACKWARD_LIMITS, "dx"), (dA, dA_w, BACKWARD_LIMITS, "dA")):
+        m = assert_limits(got, want_, limits, what)
+        for key, lim in limits.items():
+            assert m[key] <= lim, f"{what} {key}={m[key]:.3e} (limit {lim})"
+
+
 def _random_cases(n, seed):
     g = torch.Generator().manual_seed(seed)
     r = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g).item())
