@@ -54,3 +54,68 @@ def test_layers_with_identical_weights_agree():
         torch.manual_seed(42)
         outs.append(Phalanx(dim=256, length=128, dtype=torch.bfloat16).cuda()(x))
     assert torch.equal(outs[0], outs[1])
+
+
+# ------------------------------------------------------------------ numerics sweeps of tests/phalanx/test_phalanx_numerics.py
+LAYER_FORWARD_LIMITS = {"max_abs": 1e-1, "mean_abs": 1e-2, "rmse": 5e-2}      # test_phalanx_numerics.py:41-47
+LAYER_BACKWARD_LIMITS = {"max_abs": 2.2, "mean_abs": 2.2e-1, "rmse": 5e-1}    # test_phalanx_numerics.py:49-55
+
+
+def _layer_and_oracle(B, L, dim, stress, layer_seed, input_seed, kv_heads=None):
+    """bf16 layer on the kernels next to the float32 CPU oracle of the same data flow with the same (bf16) weights,
+    forward and autograd backward."""
+    import btp_oracle as O
+    from spear_b200.nn.phalanx import Phalanx
+
+    torch.manual_seed(layer_seed)
+    layer = Phalanx(dim=dim, length=L, dtype=torch.bfloat16, kv_heads=kv_heads).cuda()
+    g = torch.Generator().manual_seed(input_seed)
+    u = (torch.randn(B, L, dim, generator=g) * stress).bfloat16()
+    dout = torch.randn(B, L, dim, generator=g).bfloat16()
+    state = {k: v.float().cpu().requires_grad_(True) for k, v in layer.state_dict().items()}
+    u_ref = u.float().requires_grad_(True)
+    want = O.phalanx_forward(state, u_ref, kv_heads=kv_heads)
+    want.backward(dout.float())
+    ud = u.cuda().requires_grad_(True)
+    out = layer(ud)
+    out.backward(dout.cuda())
+    return layer, state, (out, want), (ud.grad, u_ref.grad)
+
+
+def _check(got, want, limits, what):
+    import btp_oracle as O
+
+    m = O.error_metrics(got.detach().float().cpu(), want.detach())
+    for key, lim in limits.items():
+        assert m[key] <= lim, f"{what}: {key}={m[key]:.3e} exceeds {lim:.3e}"
+
+
+def _check_param_grads(layer, state):
+    """Weight gradients are sums over all B*L tokens, so their absolute size grows with the shape and the stress
+    scale; the reference's absolute limits were set for a bf16-vs-bf16 comparison.  Against the float32 oracle
+    the meaningful bound is relative: bf16 GEMM inputs give about 1e-2."""
+    import btp_oracle as O
+
+    for name, p in layer.named_parameters():
+        rel = O.rel_l2(p.grad.float().cpu(), state[name].grad)
+        assert rel <= 3e-2, f"grad {name}: rel_l2 {rel:.3e}"
+
+
+@pytest.mark.parametrize("B,L,dim,stress", [(1, 64, 128, 1.0), (2, 128, 256, 2.0), (4, 256, 512, 3.0)])
+def test_layer_forward_and_backward_stress_across_dimensions(B, L, dim, stress):
+    """Shapes, stress scales and seeds of test_phalanx_numerics.py:120-226, forward and gradients."""
+    layer, state, (out, want), (du, du_want) = _layer_and_oracle(B, L, dim, stress, 654, 321)
+    _check(out, want, LAYER_FORWARD_LIMITS, f"out dims=({B},{L},{dim})")
+    _check(du, du_want, LAYER_BACKWARD_LIMITS, "du")
+    _check_param_grads(layer, state)
+
+
+@pytest.mark.parametrize("kv_heads_divisor", [1, 2, 4])
+def test_layer_kv_grouping(kv_heads_divisor):
+    """test_phalanx_numerics.py:234-257."""
+    dim = 256
+    kv_heads = dim // 16 // kv_heads_divisor
+    layer, state, (out, want), (du, du_want) = _layer_and_oracle(2, 128, dim, 1.0, 444, 333, kv_heads=kv_heads)
+    _check(out, want, LAYER_FORWARD_LIMITS, f"out kv_heads={kv_heads}")
+    _check(du, du_want, LAYER_BACKWARD_LIMITS, "du")
+    _check_param_grads(layer, state)
