@@ -702,6 +702,52 @@ def test_more_than_65535_sequences_and_very_long_sequences(native):
     assert_limits(dA1, dA_w, BACKWARD_LIMITS, "dA long")
 
 
+def test_tensors_beyond_4_gib(native):
+    """x, y, dy and dx of 4.8 GB each (about 21 GB on the device in all): byte offsets do not fit 32 bits.
+    Sequences from both ends and from beyond the 4 GiB mark are compared with the oracle, in the plain layout
+    (float32 and bf16 outputs) and in the gated token-major layout."""
+    B, H, L = 2304, 32, 2048
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2**30:
+        pytest.skip("needs about 25 GB of free device memory")
+    gen = torch.Generator(device="cuda").manual_seed(61)
+    x = torch.empty(B, H, 16, L, device="cuda", dtype=torch.bfloat16)
+    dy = torch.empty_like(x)
+    for t in (x, dy):  # filled in slices to keep temporaries small
+        for b0 in range(0, B, 256):
+            t[b0:b0 + 256] = (torch.randn(256, H, 16, L, device="cuda", generator=gen) * 0.5).bfloat16()
+    a = torch.sigmoid(torch.randn(B, H, L, device="cuda", generator=gen)).bfloat16()
+    assert x.numel() * 2 > 2**32
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    dA = torch.empty(B, H, L, device="cuda")
+    native.forward(a, x, y, None, 2, 32)
+    native.backward(a, x, dy, None, dx, dA, 2, 32)
+    idx = torch.tensor([0, 1, 2047, 2048, 2049, 2303])  # batch entry 2048 starts exactly at the 4 GiB mark
+    a_s, x_s, dy_s = a[idx, :2].float().cpu(), x[idx, :2].float().cpu(), dy[idx, :2].float().cpu()
+    y_w = O.btp_forward(a_s, x_s)
+    dA_w, dx_w = O.btp_backward(a_s, x_s, dy_s)
+    assert_limits(y[idx, :2].float().cpu(), y_w, FORWARD_LIMITS, "y")
+    assert_limits(dx[idx, :2].float().cpu(), dx_w, BACKWARD_LIMITS, "dx")
+    assert_limits(dA[idx, :2].cpu(), dA_w, BACKWARD_LIMITS, "dA")
+    last = slice(H - 2, H)  # the last heads of the last batch entry: the very end of every tensor
+    a_s, x_s, dy_s = a[-1:, last].float().cpu(), x[-1:, last].float().cpu(), dy[-1:, last].float().cpu()
+    dA_w, dx_w = O.btp_backward(a_s, x_s, dy_s)
+    assert_limits(y[-1:, last].float().cpu(), O.btp_forward(a_s, x_s), FORWARD_LIMITS, "y end")
+    assert_limits(dx[-1:, last].float().cpu(), dx_w, BACKWARD_LIMITS, "dx end")
+    assert_limits(dA[-1:, last].cpu(), dA_w, BACKWARD_LIMITS, "dA end")
+    del y, dx, dA
+    # gated layout: [B, L, H*16] views of the same memory (only sizes matter here)
+    v = x.reshape(B, L, H * 16)
+    bl, c = dy.reshape(B, L, H * 16), dy.flip(0).reshape(B, L, H * 16)
+    al = (torch.randn(B, L, H, device="cuda", generator=gen)).bfloat16()
+    from spear_b200.ops.btp.gated import _launch_forward
+    out = torch.empty_like(v)
+    _launch_forward(al, bl, c, v, out, 2)
+    for b in (0, 2048, 2303):
+        want = _gated_oracle(al[b:b + 1].cpu(), bl[b:b + 1].cpu(), c[b:b + 1].cpu(), v[b:b + 1].cpu())
+        assert O.rel_l2(out[b:b + 1].float().cpu(), want) <= 1e-2, f"gated out, batch entry {b}"
+
+
 def test_empty_inputs(native):
     """Empty batch / no tokens: nothing is launched, shapes and dtypes are kept, gradients are empty."""
     from spear_b200.ops.btp import btp
