@@ -746,6 +746,14 @@ def test_tensors_beyond_4_gib(native):
     for b in (0, 2048, 2303):
         want = _gated_oracle(al[b:b + 1].cpu(), bl[b:b + 1].cpu(), c[b:b + 1].cpu(), v[b:b + 1].cpu())
         assert O.rel_l2(out[b:b + 1].float().cpu(), want) <= 1e-2, f"gated out, batch entry {b}"
+    # gated backward on the full tensors against the same kernel on single batch entries
+    from spear_b200.ops.btp.gated import _backward_fused
+    del out
+    full = _backward_fused(al, bl, c, v, bl, 2)
+    for b in (0, 2048, 2303):
+        part = _backward_fused(al[b:b + 1], bl[b:b + 1], c[b:b + 1], v[b:b + 1], bl[b:b + 1], 2)
+        for f, q, name in zip(full, part, ("da_logits", "db_logits", "dc", "dv")):
+            assert O.rel_l2(f[b:b + 1].float().cpu(), q.float().cpu()) <= 2e-3, f"gated {name}, batch entry {b}"
 
 
 def test_empty_inputs(native):
