@@ -59,6 +59,7 @@ struct KernelParams {
   int total_chunks;    // BH * ncs
   int use_carry;       // k == 2
   int interleave;      // deal whole sequences round-robin to the warps (short sequences)
+  int run_len;         // forward only: > 0 deals runs of this many chunks round-robin (divides ncs); see RunCursor
 };
 
 template <int COEF>
@@ -170,6 +171,59 @@ struct WarpWork {
     }
   }
 };
+
+// Forward work list with a third mode between the two of WarpWork: RUNS of `run_len` consecutive chunks of a
+// sequence are dealt round-robin to the warps.  Few long sequences then still give every warp many units, the
+// whole GPU still reads one moving window of memory, and a carry has to be recomputed only once per run.
+//   run_len == ncs  : whole sequences round-robin (no halo at all)
+//   run_len  < ncs  : runs round-robin, a left halo at the start of every run that is not a sequence start
+//   run_len == 0    : one contiguous range per warp (halo at its first chunk only)
+struct RunCursor {
+  int bh, cs;      // current chunk
+  int left;        // chunks left in the current run, this one included (contiguous mode: never reaches 0)
+  int run, nstep;  // current run id and the distance to this warp's next run
+  int rps, len;    // runs per sequence, chunks per run
+  bool fresh;      // the current chunk starts a run (or the warp's range)
+  __device__ __forceinline__ void place() {
+    bh = run / rps;
+    cs = (run - bh * rps) * len;
+    left = len;
+    fresh = true;
+  }
+  __device__ __forceinline__ void next(int ncs) {
+    fresh = false;
+    if (--left == 0) {
+      run += nstep;
+      place();
+    } else if (++cs == ncs) {  // only a contiguous range crosses from one sequence into the next
+      cs = 0;
+      ++bh;
+    }
+  }
+};
+
+// n = number of chunks of warp `wid`; `c` is left on its first chunk.
+__device__ __forceinline__ int forward_work(long long wid, long long nwarps, const KernelParams& p, RunCursor& c) {
+  if (p.run_len > 0) {
+    c.len = p.run_len;
+    c.rps = p.ncs / p.run_len;
+    const long long total_runs = static_cast<long long>(p.total_chunks) / p.run_len;
+    c.nstep = static_cast<int>(nwarps);
+    if (wid >= total_runs) return 0;
+    c.run = static_cast<int>(wid);
+    c.place();
+    return static_cast<int>((total_runs - wid + nwarps - 1) / nwarps) * p.run_len;
+  }
+  const int first = static_cast<int>((wid * p.total_chunks) / nwarps);
+  const int n = static_cast<int>(((wid + 1) * p.total_chunks) / nwarps) - first;
+  c.bh = first / p.ncs;
+  c.cs = first - c.bh * p.ncs;
+  c.left = 0x7fffffff;
+  c.run = c.nstep = 0;
+  c.rps = c.len = 1;
+  c.fresh = true;
+  return n;
+}
 
 // Blocks in chunk `cs`.  RAGGED == false: L is a multiple of the chunk width, every chunk is full and
 // the count folds to a constant.
@@ -454,11 +508,10 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const WarpSmem<LAYOUT, STAGES> ws = carve_smem<LAYOUT, STAGES, WARPS>(smem_raw, warp);
   const TileLane tl(lane);
 
-  // contiguous range of chunks for this warp
   const long long nwarps = static_cast<long long>(gridDim.x) * WARPS;
   const long long wid = static_cast<long long>(blockIdx.x) * WARPS + warp;
-  const WarpWork work(wid, nwarps, p.total_chunks, p.ncs, p.interleave != 0);
-  const int n = work.n;
+  RunCursor cons;
+  const int n = forward_work(wid, nwarps, p, cons);
   if (n <= 0) return;
   if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled boxes need a 1024-byte aligned base
     if (lane == 0) report_error(2u, warp, 0);
@@ -477,7 +530,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   const int L = p.L, ncs = p.ncs;
   const float carry_scale = p.use_carry ? 1.0f : 0.0f;
-  ChunkCursor prod(work.bh, work.cs, work.step), cons(work.bh, work.cs, work.step);
+  RunCursor prod = cons;
   int s_prod = 0;
   auto issue = [&]() {  // starts the loads of the producer cursor's chunk into stage s_prod, then advances
     if (lane == 0) {
@@ -520,7 +573,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
-    } else if (j == 0) {
+    } else if (cons.fresh) {  // the block to the left belongs to another warp (or another run)
       halo_reduce<COEF, false, false, PRECISE>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
     }
 

@@ -214,6 +214,27 @@ bool use_interleave(const Dims& d, long long nwarps) {
   return enabled && d.BH >= 4 * nwarps;
 }
 
+// Forward work distribution (RunCursor).  Measured on B200 over L = 256 ... 65536: dealing SHORT runs of chunks
+// round-robin keeps the window of memory the whole GPU works on small, which HBM rewards more than the halo
+// per run costs: runs of 2 chunks (256 tokens) beat whole sequences by 7-11 % at L = 1024 ... 4096 and a
+// contiguous range per warp by up to 18 %; runs of 4 are 4 % better still around L = 8192; runs of 1 lose (a halo
+// per chunk).  With an odd number of chunks per sequence whole sequences are dealt when there are at least 4 per
+// warp.  Too few runs to balance (fewer than 4 per warp): one contiguous range per warp (run_len 0).
+// BTP_SM100_RUN_LEN forces a run length (0 = contiguous) for experiments.
+int forward_run_len(const Dims& d, long long nwarps) {
+  static const int forced = [] {
+    const char* e = getenv("BTP_SM100_RUN_LEN");
+    return e ? atoi(e) : -1;
+  }();
+  if (forced >= 0) return (forced > 0 && d.ncs % forced == 0) ? forced : 0;
+  if (!use_interleave(d, 0)) return 0;  // switched off by BTP_SM100_INTERLEAVE=0
+  const auto enough = [&](int r) { return static_cast<long long>(d.BH) * (d.ncs / r) >= 4 * nwarps; };
+  if (d.ncs % 4 == 0 && d.ncs > 4 && d.L >= 8192 && d.L <= 16384 && enough(4)) return 4;
+  if (d.ncs % 2 == 0 && enough(2)) return 2;
+  if (enough(d.ncs)) return d.ncs;
+  return 0;
+}
+
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 // ------------------------------------------------------------------ forward dispatch
@@ -240,7 +261,8 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
   KernelParams p{};
   p.coeff = coeff; p.x = x; p.out_f32 = y; p.ckpt = ckpt;
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
-  p.interleave = use_interleave(d, static_cast<long long>(grid) * WARPS);
+  p.run_len = forward_run_len(d, static_cast<long long>(grid) * WARPS);
+  p.interleave = p.run_len == d.ncs;
   kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_y, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
