@@ -146,7 +146,7 @@ struct ChunkCursor {
   }
 };
 
-// Which chunks a warp works on.
+// Which chunks a warp works on (backward and the gated kernels; the forward kernel uses RunCursor below).
 //   Long sequences (or too few of them to balance): a contiguous range of the (sequence, chunk) list, so
 //   that the carry runs along the sequence in registers and only the two ends of the range need a halo.
 //   Short sequences: whole sequences dealt round-robin to the warps, so that at any moment the whole GPU
