@@ -240,6 +240,34 @@ def test_checkpoint_matches_reference_layout(native):
     assert_limits(y, O.btp_forward(a, x), FORWARD_LIMITS, "y with checkpoint")
 
 
+@pytest.mark.parametrize("B,H,L", [(64, 64, 1024), (40, 64, 1664)])
+def test_forward_variants_when_runs_of_chunks_are_dealt(native, B, H, L):
+    """Shapes large enough for the forward kernel to deal runs of two chunks round-robin (each run recomputes
+    its incoming carry): float32 output, carry checkpoint, float32 and log coefficients, and k = 1, on a sample
+    of sequences against the oracle.  L = 1664 has 13 chunks per sequence, an odd number, which takes the other
+    path (a contiguous range of chunks per warp)."""
+    gen = torch.Generator(device="cuda").manual_seed(B + L)
+    x = (torch.randn(B, H, 16, L, device="cuda", generator=gen) * 0.5).bfloat16()
+    a32 = torch.sigmoid(torch.randn(B, H, L, device="cuda", generator=gen) * 1.5)
+    idx = torch.tensor([0, 1, B // 2, B - 1])
+    x_s = x[idx, :3].float().cpu()
+    for kind in ("bf16", "f32", "log"):
+        coeff = {"bf16": a32.bfloat16(), "f32": a32, "log": torch.log(a32)}[kind]
+        a_s = (a32.bfloat16().float() if kind == "bf16" else a32)[idx, :3].cpu()
+        for k in (2, 1):
+            want = O.btp_forward(a_s, x_s, k)
+            for out_dtype in (torch.bfloat16, torch.float32):
+                y = torch.empty(B, H, 16, L, device="cuda", dtype=out_dtype)
+                cp = torch.full((B, H, L // 16, 16), float("nan"), device="cuda")
+                native.forward(coeff, x, y, cp, k, 32, log_coeff=kind == "log")
+                assert_limits(y[idx, :3].float().cpu(), want, FORWARD_LIMITS, f"y {kind} k={k} {out_dtype}")
+                if k == 2:
+                    v_last = O.btp_forward(a_s, x_s, 1).reshape(4, 3, 16, L // 16, 16)[..., -1].permute(0, 1, 3, 2)
+                    got = cp[idx, :3].cpu()
+                    assert O.rel_l2(got[:, :, :-1], v_last[:, :, :-1]) < 1e-2, f"checkpoint {kind} {out_dtype}"
+                    assert torch.isnan(got[:, :, -1]).all()
+
+
 def test_outputs_stay_inside_their_buffers(native):
     """Canary words around y, dx and dA survive (stand-in for a memory checker)."""
     B, H, L = 3, 5, 144
