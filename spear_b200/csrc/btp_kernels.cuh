@@ -527,6 +527,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (!OUT_F32) prefetch_tensormap(&tm_y);
   }
   __syncwarp();
+  pdl_wait();  // nothing above touches global memory; everything below may read what the previous kernel wrote
 
   const int L = p.L, ncs = p.ncs;
   const float carry_scale = p.use_carry ? 1.0f : 0.0f;
@@ -722,6 +723,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     prefetch_tensormap(&tm_dx);
   }
   __syncwarp();
+  pdl_wait();  // nothing above touches global memory
 
   const int L = p.L, ncs = p.ncs;
   const float carry_scale = p.use_carry ? 1.0f : 0.0f;

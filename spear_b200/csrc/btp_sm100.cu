@@ -150,6 +150,36 @@ struct Launcher {
   }
 };
 
+// Launch with programmatic stream serialization: the launch of this kernel is processed while the previous
+// kernel of the stream still runs; its CTAs start when that kernel's CTAs have all exited and wait in pdl_wait()
+// until its memory is visible.  That hides the launch latency (-2 % on the forward+backward step at
+// B=1024, H=32, L=128).  The kernels do NOT release their successor early (griddepcontrol.launch_dependents at
+// kernel start was measured 9 % slower: the successor's CTAs then occupy SMs while the stragglers finish).
+// BTP_SM100_PDL=0 launches the plain way.
+bool use_pdl() {
+  static const bool v = [] {
+    const char* e = getenv("BTP_SM100_PDL");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return v;
+}
+
+template <class... Params, class... Args>
+cudaError_t launch_kernel(void (*kernel)(Params...), int grid, int threads, int smem_bytes, cudaStream_t stream,
+                          const Args&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+
 // Tuning variant (chunk width / ring depth / warps per CTA); chosen once from BTP_SM100_VARIANT.
 int variant() {
   static int v = [] {
@@ -263,8 +293,7 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
   p.run_len = forward_run_len(d, static_cast<long long>(grid) * WARPS);
   p.interleave = p.run_len == d.ncs;
-  kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_y, p);
-  BTP_CUDA_TRY(cudaGetLastError());
+  BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_y, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
 }
@@ -329,8 +358,7 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
   p.coeff = coeff; p.x = x; p.dy = dy; p.dA = dA;
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
   p.interleave = use_interleave(d, static_cast<long long>(grid) * WARPS);
-  kern<<<grid, WARPS * 32, LAYOUT::kBytes, stream>>>(tm_x, tm_dy, tm_dx, p);
-  BTP_CUDA_TRY(cudaGetLastError());
+  BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_dy, tm_dx, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
 }
