@@ -16,9 +16,11 @@
 //   * Work unit = a chunk of TL = 64*NBOX tokens of one sequence: x as NBOX TMA boxes of
 //     [16 channels x 64 tokens] bf16 (128-byte swizzle), the coefficients as one bulk copy.
 //   * Every WARP owns a private ring of STAGES chunk buffers with its own mbarriers and walks its
-//     own list of chunks (whole sequences dealt round-robin when there are many, else a contiguous
-//     range).  No block-wide or grid-wide synchronisation exists, so no warp ever waits for another
-//     warp; the only waits are on the warp's own TMA loads (bounded).
+//     own list of chunks (backward: whole sequences dealt round-robin when there are many, else a
+//     contiguous range; forward: short runs of chunks dealt round-robin, so that the whole GPU works on
+//     one small moving window of memory).  No block-wide or grid-wide synchronisation exists, so no
+//     warp ever waits for another warp; the only waits are on the warp's own TMA loads (bounded) and
+//     on the previous kernel of the stream (griddepcontrol.wait, see the launch code).
 //   * Once per chunk the warp turns the coefficients into the per-token tables the blocks need
 //     (T, P, and for backward P shifted by one token and the last Lmat row), so that the per-block
 //     work is the Lmat fragment (6 exponentials per lane), the tensor-core products and FMAs.
