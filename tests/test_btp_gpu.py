@@ -240,12 +240,12 @@ def test_checkpoint_matches_reference_layout(native):
     assert_limits(y, O.btp_forward(a, x), FORWARD_LIMITS, "y with checkpoint")
 
 
-@pytest.mark.parametrize("B,H,L", [(64, 64, 1024), (40, 64, 1664)])
+@pytest.mark.parametrize("B,H,L", [(64, 64, 1024), (40, 64, 1664), (160, 32, 464)])
 def test_forward_variants_when_runs_of_chunks_are_dealt(native, B, H, L):
     """Shapes large enough for the forward kernel to deal runs of two chunks round-robin (each run recomputes
     its incoming carry): float32 output, carry checkpoint, float32 and log coefficients, and k = 1, on a sample
     of sequences against the oracle.  L = 1664 has 13 chunks per sequence, an odd number, which takes the other
-    path (a contiguous range of chunks per warp)."""
+    path (a contiguous range of chunks per warp); L = 464 has four chunks of which the last is ragged."""
     gen = torch.Generator(device="cuda").manual_seed(B + L)
     x = (torch.randn(B, H, 16, L, device="cuda", generator=gen) * 0.5).bfloat16()
     a32 = torch.sigmoid(torch.randn(B, H, L, device="cuda", generator=gen) * 1.5)
