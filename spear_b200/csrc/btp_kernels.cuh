@@ -181,22 +181,24 @@ struct WarpWork {
 //   run_len  < ncs  : runs round-robin, a left halo at the start of every run that is not a sequence start
 //   run_len == 0    : one contiguous range per warp (halo at its first chunk only)
 struct RunCursor {
-  int bh, cs;      // current chunk
-  int left;        // chunks left in the current run, this one included (contiguous mode: never reaches 0)
-  int run, nstep;  // current run id and the distance to this warp's next run
-  int rps, len;    // runs per sequence, chunks per run
-  bool fresh;      // the current chunk starts a run (or the warp's range)
-  __device__ __forceinline__ void place() {
-    bh = run / rps;
-    cs = (run - bh * rps) * len;
-    left = len;
-    fresh = true;
-  }
+  int bh, cs;        // current chunk
+  int left;          // chunks left in the current run, this one included (contiguous mode: never reaches 0)
+  int q;             // index of the current run inside its sequence
+  int rps, len;      // runs per sequence, chunks per run
+  int dbh, dq;       // the warp's next run lies dbh sequences and dq runs further on (no division per run)
+  bool fresh;        // the current chunk starts a run (or the warp's range)
   __device__ __forceinline__ void next(int ncs) {
     fresh = false;
     if (--left == 0) {
-      run += nstep;
-      place();
+      bh += dbh;
+      q += dq;
+      if (q >= rps) {
+        q -= rps;
+        ++bh;
+      }
+      cs = q * len;
+      left = len;
+      fresh = true;
     } else if (++cs == ncs) {  // only a contiguous range crosses from one sequence into the next
       cs = 0;
       ++bh;
@@ -206,14 +208,18 @@ struct RunCursor {
 
 // n = number of chunks of warp `wid`; `c` is left on its first chunk.
 __device__ __forceinline__ int forward_work(long long wid, long long nwarps, const KernelParams& p, RunCursor& c) {
+  c.fresh = true;
   if (p.run_len > 0) {
     c.len = p.run_len;
     c.rps = p.ncs / p.run_len;
     const long long total_runs = static_cast<long long>(p.total_chunks) / p.run_len;
-    c.nstep = static_cast<int>(nwarps);
     if (wid >= total_runs) return 0;
-    c.run = static_cast<int>(wid);
-    c.place();
+    c.bh = static_cast<int>(wid / c.rps);
+    c.q = static_cast<int>(wid - static_cast<long long>(c.bh) * c.rps);
+    c.dbh = static_cast<int>(nwarps / c.rps);
+    c.dq = static_cast<int>(nwarps - static_cast<long long>(c.dbh) * c.rps);
+    c.cs = c.q * c.len;
+    c.left = c.len;
     return static_cast<int>((total_runs - wid + nwarps - 1) / nwarps) * p.run_len;
   }
   const int first = static_cast<int>((wid * p.total_chunks) / nwarps);
@@ -221,9 +227,8 @@ __device__ __forceinline__ int forward_work(long long wid, long long nwarps, con
   c.bh = first / p.ncs;
   c.cs = first - c.bh * p.ncs;
   c.left = 0x7fffffff;
-  c.run = c.nstep = 0;
+  c.q = c.dbh = c.dq = 0;
   c.rps = c.len = 1;
-  c.fresh = true;
   return n;
 }
 
