@@ -47,9 +47,9 @@ BWD_BYTES_PER_HT = 102   # coeff 2 + x 32 + dy 32 + dx 32 + dA 4
 NOMINAL_HBM_GBS = 8000.0  # the peak BASELINE.json's north star names
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload
-# (ncu capture summarised in profiles/btp_fwd_bwd_B1024_H32_L128_ncu_full.md: 276.9 MB read + 116.0 MB written;
-# the remaining 35 MB of the 151 MB of output were still in L2 when the single profiled launch ended).
-BWD_TRAFFIC_BYTES = 392_911_616
+# (ncu capture summarised in profiles/btp_fwd_bwd_B1024_H32_L128_ncu_full.md: 276.9 MB read + 117.5 MB written;
+# the remaining 33.5 MB of the 151 MB of output were still in L2 when the single profiled launch ended).
+BWD_TRAFFIC_BYTES = 394_406_144
 METRIC = "btp_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
