@@ -22,6 +22,10 @@
  *    btp_sm100_last_error() gives the detail recorded by the calling thread's
  *    most recent failing call.
  *  - Calls are re-entrant and thread-safe.
+ *  - Stream order is kept: a kernel never reads or writes memory before all earlier work in `stream` has
+ *    completed.  (The forward and backward kernels are launched with programmatic stream serialization, so
+ *    their launch may be processed while the previous kernel still runs; they wait for it before touching
+ *    memory.  Set BTP_SM100_PDL=0 in the environment for plain launches.)
  */
 #ifndef BTP_SM100_H_
 #define BTP_SM100_H_
