@@ -89,7 +89,7 @@ int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const f
  *
  * Who this is for: callers that want the reference's forward behaviour (y plus the per-block carry
  * record) but are not in a position to allocate device memory for the record at call time - a serving
- * process whose whole memory budget was handed to an arena at start-up, code running under a framework
+ * process whose whole device memory was handed to an arena at start-up, code running under a framework
  * allocator it must not bypass, a plugin that only ever receives its input and output buffers.  They pass
  * coeff, x and y exactly as for btp_sm100_forward and nothing else.
  *
