@@ -64,3 +64,64 @@ def test_sequence_sharding_on_two_gpus(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     res = json.load(open(out))
     assert all(v <= 1e-2 for v in res.values()), res
+
+
+def test_one_process_driving_two_devices():
+    """A single process alternating between cuda:0 and cuda:1 (per-device launch state, descriptors and the
+    built-in scratch of the no-allocation entry are kept per device): every call runs on the device its tensors
+    live on, whichever device is current, and both devices give the same results for the same inputs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ctypes
+
+    import btp_oracle as O
+    from spear_b200 import _lib
+    from spear_b200.nn.phalanx import Phalanx
+    from spear_b200.ops.btp import btp
+
+    g = torch.Generator().manual_seed(23)
+    B, H, L = 3, 8, 400
+    a = torch.sigmoid(torch.randn(B, H, L, generator=g)).bfloat16()
+    x = torch.randn(B, H, 16, L, generator=g).bfloat16()
+    dy = torch.randn(B, H, 16, L, generator=g).bfloat16()
+    y_w = O.btp_forward(a.float(), x.float())
+    dA_w, dx_w = O.btp_backward(a.float(), x.float(), dy.float())
+    outs = {}
+    for current, target in ((0, 1), (1, 0), (1, 1), (0, 0)):
+        torch.cuda.set_device(current)
+        dev = torch.device("cuda", target)
+        ad, xd = a.to(dev).requires_grad_(True), x.to(dev).requires_grad_(True)
+        y = btp(ad, xd, output_dtype=torch.bfloat16)
+        y.backward(dy.to(dev))
+        torch.cuda.synchronize(dev)
+        assert y.device == dev and xd.grad.device == dev
+        assert O.rel_l2(y.float().cpu(), y_w) <= 1e-2
+        assert O.rel_l2(xd.grad.float().cpu(), dx_w) <= 1e-2
+        assert O.rel_l2(ad.grad.float().cpu(), dA_w) <= 1e-2
+        outs.setdefault(target, []).append((y.detach().cpu(), xd.grad.cpu()))
+        assert torch.cuda.current_device() == current  # the call leaves the current device as it found it
+    for target in (0, 1):
+        assert torch.equal(outs[target][0][0], outs[target][1][0])
+    assert torch.equal(outs[0][0][0], outs[1][0][0]) and torch.equal(outs[0][0][1], outs[1][0][1])
+    # the no-allocation entry keeps one scratch array per device
+    lib = _lib.load()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    ys = []
+    for target in (1, 0):
+        torch.cuda.set_device(target)
+        dev = torch.device("cuda", target)
+        ad, xd = a.to(dev), x.to(dev)
+        y = torch.empty_like(xd)
+        rc = lib.btp_sm100_forward_noalloc(p(ad), p(xd), p(y), B, H, L, 2, 0, 0, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        assert rc == 0, lib.btp_sm100_last_error().decode()
+        torch.cuda.synchronize(dev)
+        ys.append(y.cpu())
+    assert torch.equal(ys[0], ys[1]) and O.rel_l2(ys[0].float(), y_w) <= 1e-2
+    # a layer on the second device while the first one is current
+    torch.cuda.set_device(0)
+    layer = Phalanx(dim=128, length=64, dtype=torch.bfloat16).to("cuda:1")
+    u = torch.randn(2, 64, 128, device="cuda:1", dtype=torch.bfloat16, requires_grad=True)
+    layer(u).sum().backward()
+    assert u.grad.device == torch.device("cuda", 1) and torch.isfinite(u.grad).all()
+    _lib.device_status()
