@@ -15,14 +15,18 @@ one JSON line.
             upload, kernels and download overlap); H2D of coeff/x/dy and D2H of y/dx/dA are
             inside the timed region.  `via_btp_autograd` is the same through `btp()` +
             autograd with plain copies on one stream.
-`roofline`  backward kernel (the dominant one): algorithmic bytes / its mean launch
-            duration, measured live with CUDA events (200 back-to-back launches of the
-            kernel between two events, right after the headline region).
-`cpu_baseline` the CPU oracle (a restatement of the reference's PyTorch path)
-            timed on this box's host cores, rank 0, N=1 only.
+            `pcie_floor_ms` is the same byte count as plain pinned copies on all ranks at once.
+`roofline`  backward kernel (the dominant one): algorithmic bytes / its launch duration,
+            measured live with CUDA events (200 back-to-back launches of the kernel between
+            two events, median of 5 repeats, right after the headline region).
+`extra`     the same kernels at the long-sequence configuration (B=16, H=64, L=8192, float32
+            log decays), at the BTP part of the sharded layer configuration (B=64, H=128,
+            L=2048) and with the headline's global batch split over the ranks (strong scaling).
+`cpu_baseline` the reference's own CPU path (spear/ops/btp/reference.py, staged under
+            oracle/_ref; the oracle port only where that is absent) timed on this box's
+            host cores, rank 0, N=1 only.
 
-`--impl reference` times the reference's CPU path instead (the oracle port:
-the reference is Python and cannot travel to the GPU box), on host cores.
+`--impl reference` times that CPU path instead, on host cores.
 """
 
 from __future__ import annotations
@@ -46,9 +50,9 @@ FWD_BYTES_PER_HT = 66    # x 32 + coeff 2 + y 32          (per head-token, bf16)
 BWD_BYTES_PER_HT = 102   # coeff 2 + x 32 + dy 32 + dx 32 + dA 4
 NOMINAL_HBM_GBS = 8000.0  # the peak BASELINE.json's north star names
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload
-# (ncu capture summarised in profiles/btp_fwd_bwd_B1024_H32_L128_ncu_full.md: 276.9 MB read + 117.5 MB written;
-# the remaining 33.5 MB of the 151 MB of output were still in L2 when the single profiled launch ended).
+# dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from an ncu capture of
+# this command with one input set: 276.9 MB read + 117.5 MB written (the remaining 33.5 MB of the 151 MB of
+# output were still in L2 when the single profiled launch ended).
 BWD_TRAFFIC_BYTES = 394_406_144
 METRIC = "btp_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
@@ -119,38 +123,71 @@ class ClockSampler:
         }
 
 
-def cpu_reference_tokens_per_s(batch: int, reps: int, warm: int):
-    """fwd+bwd of the CPU oracle (restatement of spear/ops/btp/reference.py block_two_pass_log with
-    autograd, as spear/ops/btp/runners.py:151-163 uses it) on `batch` sequences-batches of the workload."""
+def workload_string() -> str:
+    """One string for both arms, so that the two JSON lines name the same configuration."""
+    return (f"btp fwd+bwd B={B} H={H} L={L} head_dim={D} block=16 per GPU (configs[2]); "
+            "x~N(0,1/16) bf16, coeff=exp(-softplus(N(0,1))) bf16, dy~N(0,1) bf16")
+
+
+def load_cpu_reference():
+    """-> (fwd_bwd(a, x, dy), kind, what).
+
+    kind "reference": the reference's own spear/ops/btp/reference.py, staged unmodified under oracle/_ref by
+    oracle/stage_reference.py and loaded by file path (the package itself would import the compiled
+    extension); block_two_pass_log with autograd, as spear/ops/btp/runners.py:151-163 drives it.
+    kind "port": oracle/btp_oracle.py, only where the reference has not been staged."""
+    ref_py = os.path.join(ROOT, "oracle", "_ref", "spear", "ops", "btp", "reference.py")
+    if os.path.exists(ref_py):
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("spear_reference_math", ref_py)
+        R = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(R)
+
+        def fwd_bwd(a, x, dy):
+            a = a.detach().clone().requires_grad_(True)
+            x = x.detach().clone().requires_grad_(True)
+            y = R.block_two_pass_log(a, x, 16)
+            (y * dy).sum().backward()
+            return y.detach(), a.grad, x.grad
+
+        return fwd_bwd, "reference", "spear/ops/btp/reference.py block_two_pass_log + autograd (the reference's own code)"
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import btp_oracle as O
 
+    return (lambda a, x, dy: O.btp_forward_backward_autograd(a, x, dy, "log")), "port", \
+        "oracle/btp_oracle.py (restatement of block_two_pass_log) + autograd"
+
+
+def cpu_reference_times(batch: int, reps: int, warm: int):
+    """Seconds per fwd+bwd of the CPU path over `batch` batch entries of the workload -> (times, kind, what)."""
+    fwd_bwd, kind, what = load_cpu_reference()
     # all the host threads this process may use (torchrun presets OMP_NUM_THREADS=1)
     torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     g = torch.Generator().manual_seed(0)
-    a = torch.sigmoid(torch.randn(batch, H, L, generator=g))
-    x = torch.randn(batch, H, D, L, generator=g) * 0.25
-    dy = torch.randn(batch, H, D, L, generator=g)
+    a = torch.exp(-torch.nn.functional.softplus(torch.randn(batch, H, L, generator=g))).bfloat16().float()
+    x = (torch.randn(batch, H, D, L, generator=g) * 0.25).bfloat16().float()
+    dy = torch.randn(batch, H, D, L, generator=g).bfloat16().float()
     times = []
     for i in range(warm + reps):
         t0 = time.perf_counter()
-        O.btp_forward_backward_autograd(a, x, dy, "log")
+        fwd_bwd(a, x, dy)
         t1 = time.perf_counter()
         if i >= warm:
             times.append(t1 - t0)
-    return times
+    return times, kind, what
 
 
 def run_reference_arm(args, rank):
-    """The reference's CPU path (oracle port) on this box's host cores; rank 0 only."""
+    """The reference's CPU path on this box's host cores; rank 0 only."""
     if rank != 0:
         return
     # size the per-step sample so that the whole run stays within about two minutes
-    probe = min(cpu_reference_tokens_per_s(8, 1, 1))
+    probe = min(cpu_reference_times(8, 1, 1)[0])
     per_seq = probe / 8
     seconds_per_step = 120.0 / max(1, args.steps + args.warmup)
     batch = int(max(1, min(B, seconds_per_step / per_seq)))
-    times = cpu_reference_tokens_per_s(batch, args.steps, args.warmup)
+    times, kind, what = cpu_reference_times(batch, args.steps, args.warmup)
     threads = torch.get_num_threads()
     total = sum(times)
     value = batch * L * len(times) / total
@@ -159,10 +196,10 @@ def run_reference_arm(args, rank):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"btp fwd+bwd B={B} H={H} L={L} head_dim={D} block=16 (configs[2])",
-                   "step": f"CPU fwd+bwd over a sample of {batch} of the {B} batch entries"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{batch}/{B} batch entries per step, {len(times)} steps, float32, torch CPU autograd"},
+        "config": {"workload": workload_string(),
+                   "step": f"CPU fwd+bwd over a sample of {batch} of the {B} batch entries; {what}"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": f"{batch}/{B} batch entries per step, {len(times)} steps, float32 (bf16-rounded inputs), torch CPU autograd"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -178,8 +215,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configurations and the strong-scaling line")
     ap.add_argument("--batch", type=int, default=B, help="batch entries per GPU (default: the benchmark workload)")
     ap.add_argument("--sets", type=int, default=3, help="rotating input/output sets")
+    ap.add_argument("--kernel-launches", type=int, default=200, help="launches per per-kernel timing loop")
+    ap.add_argument("--kernel-repeats", type=int, default=5, help="repeats of each per-kernel timing loop")
     args = ap.parse_args()
 
     B = args.batch
@@ -209,29 +249,59 @@ def main():
 
     from spear_b200 import _btp, _lib
     from spear_b200.ops.btp import btp
+    from spear_b200.sharding import batch_shard, max_over_ranks, sum_over_ranks
 
     _lib.load()
     dev = torch.device("cuda", local_rank)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
 
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def over_ranks_max(values):
+        return max_over_ranks(values, device=dev) if dist is not None else [float(v) for v in values]
+
+    def make_sets(nb, heads, length, nsets, coeff="bf16"):
+        """nsets rotating (coeff, x, dy, y, dx, dA) tuples in the benchmark's distributions."""
+        out = []
+        for _ in range(nsets):
+            x = (torch.randn(nb, heads, D, length, device=dev, generator=gen) * 0.25).bfloat16()
+            if coeff == "bf16":  # a = exp(-softplus(N(0,1))), the linear 16-bit form the reference op takes
+                a = torch.exp(-torch.nn.functional.softplus(torch.randn(nb, heads, length, device=dev, generator=gen))).bfloat16()
+            else:                # "f32log": log a ~ U(-1e-3, 0) in float32 (decays bf16 cannot hold)
+                a = -1e-3 * torch.rand(nb, heads, length, device=dev, generator=gen)
+            dy = torch.randn(nb, heads, D, length, device=dev, generator=gen).bfloat16()
+            out.append((a, x, dy, torch.empty_like(x), torch.empty_like(x), torch.empty(nb, heads, length, device=dev)))
+        return out
+
+    def loop_us(launch, n, repeats):
+        """n back-to-back launches between two CUDA events on the launching stream, `repeats` times ->
+        us per launch of every repeat.  This is the kernel's launch duration the way it runs in a step loop
+        (launch latency hidden behind the previous kernel)."""
+        res = []
+        for i in range(3):
+            launch(i)
+        for _ in range(repeats):
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            g0.record()
+            for i in range(n):
+                launch(i)
+            g1.record()
+            torch.cuda.synchronize()
+            res.append(g0.elapsed_time(g1) / n * 1e3)
+        return res
+
     # ---- inputs resident in HBM; NSETS rotating sets (each step touches 705 MB, the L2 holds 126 MB)
     NSETS = max(1, args.sets)
-    sets = []
-    for _ in range(NSETS):
-        x = (torch.randn(B, H, D, L, device=dev, generator=gen) * 0.25).bfloat16()
-        a = torch.exp(-torch.nn.functional.softplus(torch.randn(B, H, L, device=dev, generator=gen))).bfloat16()
-        dy = torch.randn(B, H, D, L, device=dev, generator=gen).bfloat16()
-        sets.append((a, x, dy, torch.empty_like(x), torch.empty_like(x), torch.empty(B, H, L, device=dev)))
+    sets = make_sets(B, H, L, NSETS)
 
     def step(i):
         a, x, dy, y, dx, dA = sets[i % NSETS]
         _btp.forward(a, x, y, None, 2, 32)
         _btp.backward(a, x, dy, None, dx, dA, 2, 32)
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
 
     for i in range(args.warmup):
         step(i)
@@ -251,23 +321,9 @@ def main():
     launches = _lib.launch_count() - launches0
     total_ms = e0.elapsed_time(e1)
 
-    # ---- per-kernel durations, live (a second pass, so that no event record sits inside the headline region).
-    #      (a) nk launches of ONE kernel back to back between two events: total / nk is that kernel's average
-    #          launch duration the way it runs in the step loop (launch latency hidden behind the previous kernel);
-    #      (b) an event on either side of every single launch: includes the launch latency that the event records
-    #          expose, reported beside (a) for reference.
-    nk = min(args.steps, 200)
-
-    def same_kernel_loop(launch):
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for i in range(3):
-            launch(i)
-        g0.record()
-        for i in range(nk):
-            launch(i)
-        g1.record()
-        torch.cuda.synchronize()
-        return g0.elapsed_time(g1) / nk * 1e3
+    # ---- per-kernel durations, live (a second pass, so that no event record sits inside the headline region):
+    #      a fixed number of launches per loop whatever --steps is, several repeats, median and best reported.
+    nk, reps = max(1, args.kernel_launches), max(1, args.kernel_repeats)
 
     def launch_fwd(i):
         a, x, dy, y, dx, dA = sets[i % NSETS]
@@ -277,8 +333,10 @@ def main():
         a, x, dy, y, dx, dA = sets[i % NSETS]
         _btp.backward(a, x, dy, None, dx, dA, 2, 32)
 
-    fwd_us = same_kernel_loop(launch_fwd)
-    bwd_us = same_kernel_loop(launch_bwd)
+    fwd_runs = loop_us(launch_fwd, nk, reps)
+    bwd_runs = loop_us(launch_bwd, nk, reps)
+    fwd_us, bwd_us = statistics.median(fwd_runs), statistics.median(bwd_runs)
+    # an event on either side of every single launch: includes the launch latency that the records expose
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(nk)]
     for i in range(nk):
         evs[i][0].record()
@@ -292,7 +350,7 @@ def main():
     bwd_single_us = statistics.mean(e[1].elapsed_time(e[2]) for e in evs) * 1e3
     _lib.device_status()
 
-    # ---- timed region 2: end to end through btp() with pinned host buffers
+    # ---- timed region 2: end to end with pinned host buffers
     ha = sets[0][0].cpu().pin_memory()
     hx = sets[0][1].cpu().pin_memory()
     hdy = sets[0][2].cpu().pin_memory()
@@ -314,8 +372,27 @@ def main():
 
     from spear_b200.ops.btp import btp_fwd_bwd_host
 
-    def e2e_step_pipelined():  # the host-buffer entry of the package: three streams, batch in slices
+    def e2e_step_pipelined():  # the host-buffer entry of the package
         btp_fwd_bwd_host(ha, hx, hdy, hy, hdx, hdA, k=2)
+
+    # the floor the link sets: the step's bytes as plain pinned copies, both directions at once on two streams,
+    # on every rank at the same time (no kernels)
+    s_up, s_down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    d_in = [torch.empty_like(t, device=dev) for t in (ha, hx, hdy)]
+    d_out = [torch.empty_like(t, device=dev) for t in (hy, hdx, hdA)]
+
+    def copies_only():
+        cur = torch.cuda.current_stream(dev)
+        s_up.wait_stream(cur)
+        s_down.wait_stream(cur)
+        with torch.cuda.stream(s_up):
+            for d, h in zip(d_in, (ha, hx, hdy)):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(s_down):
+            for d, h in zip(d_out, (hy, hdx, hdA)):
+                h.copy_(d, non_blocking=True)
+        cur.wait_stream(s_up)
+        cur.wait_stream(s_down)
 
     def time_e2e(fn):
         for _ in range(3):
@@ -329,17 +406,72 @@ def main():
         barrier()
         return f0.elapsed_time(f1)
 
-    e2e_ms = e2e_autograd_ms = float("nan")
+    e2e_ms = e2e_autograd_ms = floor_ms = float("nan")
     if args.e2e_steps > 0:
         e2e_autograd_ms = time_e2e(e2e_step)
         e2e_ms = time_e2e(e2e_step_pipelined)
+        floor_ms = time_e2e(copies_only)
+    del d_in, d_out
+
+    # ---- the other benchmark configurations and the strong-scaling line (extra keys; the headline stays as it is)
+    extra = {}
+    if not args.no_extra:
+        del sets
+        torch.cuda.empty_cache()
+        n_x = max(20, nk // 2)
+
+        def plain_pair(nb, heads, length, coeff, log_coeff):
+            ss = make_sets(nb, heads, length, 2, coeff)
+
+            def f(i):
+                a, x, dy, y, dx, dA = ss[i % 2]
+                _btp.forward(a, x, y, None, 2, 32, log_coeff=log_coeff)
+
+            def b(i):
+                a, x, dy, y, dx, dA = ss[i % 2]
+                _btp.backward(a, x, dy, None, dx, dA, 2, 32, log_coeff=log_coeff)
+
+            def fb(i):
+                f(i)
+                b(i)
+
+            r = [statistics.median(loop_us(fn, n_x, 3)) for fn in (f, b, fb)]
+            del ss
+            torch.cuda.empty_cache()
+            return r
+
+        # configs[3]: long sequences, near-unit decays given as float32 log a (4 more bytes per head-token)
+        f3, b3, s3 = over_ranks_max(plain_pair(16, 64, 8192, "f32log", True))
+        # the BTP part of configs[4] (Phalanx layer, dim 2048, L 2048, global batch 64) in the plain layout
+        nb4 = 64
+        f4, b4, s4 = over_ranks_max(plain_pair(nb4, 128, 2048, "bf16", False))
+        # strong scaling of the headline workload: the global batch of 1024 split over the ranks
+        lo, hi = batch_shard(1024, rank, world)
+        fs, bs, ss_ = over_ranks_max(plain_pair(hi - lo, H, L, "bf16", False))
+        _lib.device_status()
+        extra = {"world": world, "loop": f"{n_x} launches between two CUDA events, median of 3, slowest rank; 2 rotating sets"}
+
+        def cfg_line(label, nb, heads, length, fb_, bb_, f_us, b_us, s_us):
+            ht_ = nb * heads * length
+            return {"workload": label, "fwd_us": f_us, "bwd_us": b_us, "fwd_bwd_us": s_us,
+                    "fwd_gbs": fb_ * ht_ / f_us / 1e3, "bwd_gbs": bb_ * ht_ / b_us / 1e3,
+                    "fwd_bwd_gbs": (fb_ + bb_) * ht_ / s_us / 1e3,
+                    "tokens_per_s_per_gpu": nb * length / (s_us * 1e-6)}
+
+        extra["configs3"] = cfg_line("btp fwd+bwd B=16 H=64 L=8192 per GPU, float32 log a ~ U(-1e-3,0), bf16 x/dy",
+                                     16, 64, 8192, FWD_BYTES_PER_HT + 2, BWD_BYTES_PER_HT + 2, f3, b3, s3)
+        extra["configs4_btp_part"] = cfg_line("btp fwd+bwd B=64 H=128 L=2048 per GPU, bf16 (plain layout)",
+                                              nb4, 128, 2048, FWD_BYTES_PER_HT, BWD_BYTES_PER_HT, f4, b4, s4)
+        extra["strong_scaling"] = {
+            "workload": f"btp fwd+bwd global B=1024 H={H} L={L} split over {world} GPU(s)", "batch_per_gpu": hi - lo,
+            "fwd_us": fs, "bwd_us": bs, "fwd_bwd_us": ss_, "tokens_per_s": 1024 * L / (ss_ * 1e-6),
+            "limiter": "per-launch host cost and launch latency once a rank's share drops below a few hundred sequences per SM wave",
+        }
 
     # ---- max over ranks
     if dist is not None:
-        from spear_b200.sharding import max_over_ranks, sum_over_ranks
-
-        total_ms, e2e_ms, e2e_autograd_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us = max_over_ranks(
-            [total_ms, e2e_ms, e2e_autograd_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us], device=dev)
+        total_ms, e2e_ms, e2e_autograd_ms, floor_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us = max_over_ranks(
+            [total_ms, e2e_ms, e2e_autograd_ms, floor_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us], device=dev)
         launches = int(sum_over_ranks([launches], device=dev)[0])
 
     if rank == 0:
@@ -350,19 +482,26 @@ def main():
         step_us = total_ms * 1e3 / args.steps
         step_gbs = (FWD_BYTES_PER_HT + BWD_BYTES_PER_HT) * ht / (step_us * 1e-6) / 1e9
         value = world * B * L * args.steps / (total_ms * 1e-3)
+        for v in extra.values():
+            if isinstance(v, dict) and "fwd_gbs" in v:
+                for key in ("fwd", "bwd", "fwd_bwd"):
+                    v[key + "_frac_of_measured"] = v[key + "_gbs"] / peak
+        e2e_value = world * B * L * args.e2e_steps / (e2e_ms * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {
-                "workload": f"btp fwd+bwd B={B} H={H} L={L} head_dim={D} block=16 per GPU (configs[2]); "
-                            "x~N(0,1/16) bf16, coeff=exp(-softplus(N(0,1))) bf16, dy~N(0,1) bf16",
+                "workload": workload_string(),
                 "l2": f"each step touches {168 * B * H * L / 1e6:.0f} MB (L2 holds 126 MB) and {NSETS} input/output sets rotate",
                 "parallelism": f"batch sharded over {world} GPU(s), no data-path collective",
             },
-            "e2e": {"value": world * B * L * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "api": "spear_b200.ops.btp.btp_fwd_bwd_host (pinned host tensors in and out, 8 batch slices on 3 streams)",
+            "e2e": {"value": e2e_value, "unit": UNIT, "per_gpu": e2e_value / world,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / max(1, args.e2e_steps),
+                    "pcie_floor_ms": floor_ms / max(1, args.e2e_steps),
+                    "pcie_floor": f"the same bytes as plain pinned copies, both directions at once, on all {world} rank(s) at the same time",
+                    "frac_of_pcie_floor": floor_ms / e2e_ms,
+                    "api": "spear_b200.ops.btp.btp_fwd_bwd_host (pinned host tensors in and out, batch slices on 3 streams)",
                     "via_btp_autograd": {"value": world * B * L * args.e2e_steps / (e2e_autograd_ms * 1e-3), "unit": UNIT,
                                          "api": "tensor.to(device) + btp() + backward() + copy_ to host, one stream"}},
             "gpu_launches": launches,
@@ -370,23 +509,28 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "btp_backward_kernel", "achieved": bwd_gbs, "peak": peak,
                          "unit": "GB/s", "frac": bwd_gbs / peak,
                          "traffic": BWD_TRAFFIC_BYTES if (B, H, L) == (1024, 32, 128) else None,
-                         "peak_kind": f"of {peak_kind}", "us_per_launch": bwd_us,
+                         "peak_kind": f"of {peak_kind}", "us_per_launch": bwd_us, "us_per_launch_best": min(bwd_runs),
+                         "us_per_launch_runs": bwd_runs,
                          "us_per_launch_between_event_records": bwd_single_us,
-                         "method": f"{nk} back-to-back launches of the kernel between two CUDA events on the launching stream",
+                         "method": f"{nk} back-to-back launches of the kernel between two CUDA events on the launching stream, "
+                                   f"median of {reps} repeats",
                          "algorithmic_bytes_per_launch": BWD_BYTES_PER_HT * ht},
             "roofline_forward": {"bound": "hbm", "kernel": "btp_forward_kernel", "achieved": fwd_gbs, "peak": peak,
                                  "unit": "GB/s", "frac": fwd_gbs / peak, "us_per_launch": fwd_us,
+                                 "us_per_launch_best": min(fwd_runs), "us_per_launch_runs": fwd_runs,
                                  "us_per_launch_between_event_records": fwd_single_us,
                                  "algorithmic_bytes_per_launch": FWD_BYTES_PER_HT * ht},
             "step_hbm": {"achieved_gbs": step_gbs, "frac_of_measured": step_gbs / peak,
                          "frac_of_nominal_8TBs": step_gbs / NOMINAL_HBM_GBS, "us_per_step": step_us},
         }
+        if extra:
+            line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
             nb = B  # the full batch: a few seconds of CPU work per repetition
-            times = cpu_reference_tokens_per_s(nb, 3, 1)
+            times, kind, what = cpu_reference_times(nb, 3, 1)
             line["cpu_baseline"] = {
-                "value": nb * L / min(times), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"{nb}/{B} batch entries, fwd+bwd float32 torch CPU autograd, best of 3 after 1 warm-up",
+                "value": nb * L / min(times), "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+                "sample": f"{nb}/{B} batch entries, fwd+bwd float32 torch CPU autograd, best of 3 after 1 warm-up; {what}",
             }
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:

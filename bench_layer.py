@@ -1,8 +1,8 @@
 """Timing of the gated (token-major) op and of the whole Phalanx layer, on one GPU or batch-sharded over several.
 
-    python -m spear_b200.bench_layer [--batch 1024 --length 128 --dim 512] [--steps 50] [--what gated|layer|both]
+    python bench_layer.py [--batch 1024 --length 128 --dim 512] [--steps 50] [--what gated|layer|both]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        -m spear_b200.bench_layer --what layer --batch 64 --length 2048 --dim 2048 --decay-mix
+        bench_layer.py --what layer --batch 64 --length 2048 --dim 2048 --decay-mix
 
 Under torch.distributed.run `--batch` is the GLOBAL batch: each rank takes its slice (strong scaling, no
 exchange on the forward/backward data path), times are the maximum over ranks and rank 0 prints.  With
@@ -21,8 +21,11 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 GATED_FWD_BYTES = 130  # per head-token: A 2 + B 32 + C 32 + V 32 read, out 32 written
 GATED_BWD_BYTES = 228  # A 2 + B, C, V, dOut 128 read; dA 2 + dB, dC, dV 96 written
@@ -61,7 +64,7 @@ def bench_gated(B, L, H, steps, sets):
     def bwd():
         al, bl, c, v, do, out = data[i[0] % sets]
         i[0] += 1
-        G._backward_fused(al, bl, c, v, do, 2)
+        G._backward(al, bl, c, v, do, 2)
 
     ht = B * L * H
     tf, tb = _timed(fwd, steps), _timed(bwd, steps)

@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define BTP_SM100_ABI_VERSION 1
+#define BTP_SM100_ABI_VERSION 2
 
 /* status codes */
 #define BTP_OK 0
@@ -96,6 +96,7 @@ int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const f
  * The record goes to a fixed array of BTP_SM100_NOALLOC_MAX_HEAD_TOKENS floats (4 MiB) that every GPU
  * holds from the moment it loads the library until the process exits.  The call returns
  * BTP_ERR_TOO_LARGE when B*H*L exceeds that number; use btp_sm100_forward with your own buffer then.
+ * (With k == 1 there is no carry and no record: the array is not touched and the limit does not apply.)
  * The entry point itself never calls cudaMalloc, cudaFree or any other allocating routine.
  *
  * First call on each device: it looks up the device address of the array (one cudaGetSymbolAddress with
@@ -107,6 +108,15 @@ int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const f
 #define BTP_SM100_NOALLOC_MAX_HEAD_TOKENS (1 << 20)
 int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, int H, int L, int k,
                               int coeff_dtype, int out_dtype, void* stream);
+
+/*
+ * Copies the first n_floats of the record that btp_sm100_forward_noalloc keeps inside the library into `dst`
+ * (device memory of the caller, current device), in stream order.  No counterpart in the reference.  The layout
+ * is the checkpoint's, [B, H, L/16, 16] of the last btp_sm100_forward_noalloc call with k == 2 on this device; a
+ * caller that wants the record (the reference's backward reads it, btp-backwards.cu:374-378) fetches it here, and
+ * the tests use it to check that the kernel really wrote to this device's copy of the array.  Allocates nothing.
+ */
+int btp_sm100_noalloc_read_record(float* dst, long long n_floats, void* stream);
 
 /*
  * Gated forward in token-major layout: the Phalanx layer's glue fused around the op.
@@ -185,6 +195,24 @@ const char* btp_sm100_last_error(void);
  * Not on the hot path: the forward/backward calls themselves never synchronise.
  */
 int btp_sm100_device_status(void* stream, unsigned int* detail);
+
+/*
+ * How long a wait inside a kernel may last before the kernel gives up, records the error word that
+ * btp_sm100_device_status reports, lets its copies in flight land and returns (default 2 s; 0 restores the
+ * default).  Applies to the forward and backward launches that follow, process-wide.  Returns the previous
+ * value.  No counterpart in the reference, whose kernels wait on cluster barriers without a bound
+ * (csrc/btp/btp-forward.cu:340-347).
+ */
+unsigned long long btp_sm100_set_wait_limit(unsigned long long ns);
+
+/*
+ * Test hook for the give-up path, no counterpart in the reference: the NEXT forward or backward launch makes
+ * warp 0 of block 0 expect `bytes` more bytes on its first load barrier than its loads deliver, so that this
+ * one wait runs out.  The kernel then behaves as documented for a timeout: it returns normally, the chunks of
+ * that warp stay unwritten, btp_sm100_device_status reports BTP_ERR_DEVICE_TIMEOUT once.  Nothing faults or
+ * hangs; combine it with a short btp_sm100_set_wait_limit so that the test takes milliseconds.
+ */
+void btp_sm100_test_expect_missing_bytes(unsigned int bytes);
 
 /* Number of kernels this library has launched in this process (all threads). */
 unsigned long long btp_sm100_launch_count(void);

@@ -199,8 +199,14 @@ def error_metrics(got: torch.Tensor, want: torch.Tensor, eps: float = 1e-7) -> d
     }
 
 
-def phalanx_forward(state: dict, u: torch.Tensor, k: int = 2, kv_heads: int | None = None) -> torch.Tensor:
+def phalanx_forward(state: dict, u: torch.Tensor, k: int = 2, kv_heads: int | None = None,
+                    decay_dtype: torch.dtype | None = None) -> torch.Tensor:
     """The Phalanx layer's data flow around the oracle op, in the dtype of `u` on CPU.
+
+    `decay_dtype`: the reference layer computes its projections and the sigmoid in bfloat16
+    (spear/nn/phalanx/swr.py:146,170,216), so the decay it hands to the op is a bfloat16 number.  Decays close
+    to one (0.9995) do not survive that rounding; passing torch.bfloat16 here rounds A the same way (gradients
+    pass straight through the rounding), so that a higher-precision evaluation still sees the layer's decays.
 
     Follows spear/nn/phalanx/swr.py:157-175 (the four projections), :96-103 (head h reads key/value head
     h // (heads / kv_heads)), :196-221 (A = sigmoid, X = sigmoid(B) * V), :311-327 (y * C + V, output
@@ -216,6 +222,8 @@ def phalanx_forward(state: dict, u: torch.Tensor, k: int = 2, kv_heads: int | No
     idx = torch.arange(H) // (H // KV)
     heads = lambda t, n: t.transpose(1, 2).reshape(Bsz, n, D, L)
     A = torch.sigmoid(lin("proj_a", u)).transpose(1, 2)
+    if decay_dtype is not None:
+        A = A + (A.to(decay_dtype).to(A.dtype) - A).detach()
     Bg = heads(lin("proj_b", u), KV).index_select(1, idx)
     C = heads(lin("proj_c", u), KV).index_select(1, idx)
     V = heads(lin("proj_v", u), H)

@@ -19,7 +19,7 @@ DTYPE_BF16 = 0
 DTYPE_F32 = 1
 DTYPE_F32_LOG = 2
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # every symbol include/btp_sm100.h declares: name -> (restype, argtypes)
 _vp, _i, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
@@ -31,6 +31,9 @@ SYMBOLS = {
     "btp_sm100_gated_backward": (_i, [_vp] * 9 + [_i, _i, _i] + [_ll] * 9 + [_i, _vp]),
     "btp_sm100_decode_step": (_i, [_vp] * 11 + [_ll, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_prefill_state": (_i, [_vp] * 5 + [_ll, _i, _i, _i, _i, _vp]),
+    "btp_sm100_noalloc_read_record": (_i, [_vp, _ll, _vp]),
+    "btp_sm100_set_wait_limit": (ctypes.c_ulonglong, [ctypes.c_ulonglong]),
+    "btp_sm100_test_expect_missing_bytes": (None, [ctypes.c_uint]),
     "btp_sm100_status_string": (ctypes.c_char_p, [_i]),
     "btp_sm100_last_error": (ctypes.c_char_p, []),
     "btp_sm100_device_status": (_i, [_vp, ctypes.POINTER(ctypes.c_uint)]),

@@ -44,7 +44,7 @@ constexpr int kCoefF32Log = 2;  // natural-log coefficient, float
 constexpr float kLog2E = 1.4426950408889634f;
 constexpr float kZeroLog2 = -200.0f;  // stands in for log2(0): 2^-200 flushes to zero, sums stay finite
 constexpr float kTinyCoeff = 1e-9f;   // coefficients at or below this count as zero (btp-forward.cu:179)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // bounded waits give up after 2 s
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default: bounded waits give up after 2 s
 
 // Error word written when a bounded wait gives up: {code, blockIdx.x, warp, chunk}.
 __device__ unsigned int g_btp_device_error[4];
@@ -62,6 +62,8 @@ struct KernelParams {
   int use_carry;       // k == 2
   int interleave;      // deal whole sequences round-robin to the warps (short sequences)
   int run_len;         // forward only: > 0 deals runs of this many chunks round-robin (divides ncs); see RunCursor
+  unsigned long long wait_limit_ns;  // bounded waits give up after this long (btp_sm100_set_wait_limit)
+  unsigned int test_missing_tx;      // test hook: warp 0 of block 0 expects this many bytes that never arrive
 };
 
 template <int COEF>
@@ -532,6 +534,8 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     fence_proxy_async_smem();
     prefetch_tensormap(&tm_x);
     if (!OUT_F32) prefetch_tensormap(&tm_y);
+    // test hook for the give-up path: bytes that no copy will ever deliver keep this warp's first wait pending
+    if (p.test_missing_tx != 0 && blockIdx.x == 0 && warp == 0) mbar_expect_tx(ws.bar(0), p.test_missing_tx);
   }
   __syncwarp();
   pdl_wait();  // nothing above touches global memory; everything below may read what the previous kernel wrote
@@ -570,7 +574,8 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       if (!OUT_F32 && lane == 0) bulk_wait_group_read<1>();  // the store that last used that stage has drained
       issue();
     }
-    if (!mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs)) {
+    // the decision to give up is taken by the whole warp: the code below is full of warp-wide instructions
+    if (!__all_sync(0xffffffffu, mbar_wait_bounded(ws.bar(s), phase, p.wait_limit_ns))) {
       failed = true;
       break;
     }
@@ -674,7 +679,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (lane == 0) report_error(1u, warp, cons.bh * ncs + cons.cs);
     // give the loads still in flight a (bounded) chance to land before the buffers are released
     for (int k = j; k < n && k <= j + AHEAD; ++k) {
-      mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs);
+      mbar_wait_bounded(ws.bar(s), phase, p.wait_limit_ns);
       if (++s == STAGES) {
         s = 0;
         phase ^= 1u;
@@ -728,6 +733,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_dy);
     prefetch_tensormap(&tm_dx);
+    if (p.test_missing_tx != 0 && blockIdx.x == 0 && warp == 0) mbar_expect_tx(ws.bar(0), p.test_missing_tx);  // see forward
   }
   __syncwarp();
   pdl_wait();  // nothing above touches global memory
@@ -906,7 +912,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   int j = 0, s = 0, d = 0, tset = 0;
   uint32_t phase = 0;
   for (; j < n; ++j) {
-    if (!mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs)) {
+    if (!__all_sync(0xffffffffu, mbar_wait_bounded(ws.bar(s), phase, p.wait_limit_ns))) {  // warp-uniform, as in forward
       failed = true;
       break;
     }
@@ -982,7 +988,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   if (failed) {
     if (lane == 0) report_error(1u, warp, cons.bh * ncs + cons.cs);
     for (int k = j; k < issued; ++k) {
-      mbar_wait_bounded(ws.bar(s), phase, kWaitLimitNs);
+      mbar_wait_bounded(ws.bar(s), phase, p.wait_limit_ns);
       if (++s == STAGES) {
         s = 0;
         phase ^= 1u;

@@ -21,6 +21,8 @@ using namespace btp;
 
 thread_local char tls_error[512] = "";
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<unsigned long long> g_wait_limit_ns{btp::kWaitLimitNs};  // btp_sm100_set_wait_limit
+std::atomic<unsigned int> g_test_missing_tx{0};                      // btp_sm100_test_expect_missing_bytes, one launch
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -180,33 +182,6 @@ cudaError_t launch_kernel(void (*kernel)(Params...), int grid, int threads, int 
   return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
 }
 
-// Tuning variant (chunk width / ring depth / warps per CTA); chosen once from BTP_SM100_VARIANT.
-int variant() {
-  static int v = [] {
-    const char* e = getenv("BTP_SM100_VARIANT");
-    return e ? atoi(e) : 0;
-  }();
-  return v;
-}
-
-// Backward with the Lmat operand split into two bf16 terms (BTP_SM100_PRECISE_BWD=0 selects the single-term
-// kernel, which is about a tenth faster and leaves dA at the accuracy of a bf16 Lmat).
-bool precise_backward() {
-  static const bool v = [] {
-    const char* e = getenv("BTP_SM100_PRECISE_BWD");
-    return e ? atoi(e) != 0 : true;
-  }();
-  return v;
-}
-
-bool precise_forward() {
-  static const bool v = [] {
-    const char* e = getenv("BTP_SM100_PRECISE_FWD");
-    return e ? atoi(e) != 0 : true;
-  }();
-  return v;
-}
-
 struct Dims {
   int B, H, L;
   long long BH;
@@ -236,13 +211,7 @@ int set_chunks(const char* fn, Dims* d, int TL) {
 
 // Whole sequences are dealt round-robin to the warps when they are numerous enough (at least 4 per warp) for
 // that to balance; otherwise every warp takes a contiguous range of chunks.
-bool use_interleave(const Dims& d, long long nwarps) {
-  static const bool enabled = [] {
-    const char* e = getenv("BTP_SM100_INTERLEAVE");
-    return e ? atoi(e) != 0 : true;
-  }();
-  return enabled && d.BH >= 4 * nwarps;
-}
+bool use_interleave(const Dims& d, long long nwarps) { return d.BH >= 4 * nwarps; }
 
 // Forward work distribution (RunCursor).  Measured on B200 over L = 256 ... 65536: dealing SHORT runs of chunks
 // round-robin keeps the window of memory the whole GPU works on small, which HBM rewards more than the halo
@@ -250,14 +219,7 @@ bool use_interleave(const Dims& d, long long nwarps) {
 // contiguous range per warp by up to 18 %; runs of 4 are 4 % better still around L = 8192; runs of 1 lose (a halo
 // per chunk).  With an odd number of chunks per sequence whole sequences are dealt when there are at least 4 per
 // warp.  Too few runs to balance (fewer than 4 per warp): one contiguous range per warp (run_len 0).
-// BTP_SM100_RUN_LEN forces a run length (0 = contiguous) for experiments.
 int forward_run_len(const Dims& d, long long nwarps) {
-  static const int forced = [] {
-    const char* e = getenv("BTP_SM100_RUN_LEN");
-    return e ? atoi(e) : -1;
-  }();
-  if (forced >= 0) return (forced > 0 && d.ncs % forced == 0) ? forced : 0;
-  if (!use_interleave(d, 0)) return 0;  // switched off by BTP_SM100_INTERLEAVE=0
   const auto enough = [&](int r) { return static_cast<long long>(d.BH) * (d.ncs / r) >= 4 * nwarps; };
   if (d.ncs % 4 == 0 && d.ncs > 4 && d.L >= 8192 && d.L <= 16384 && enough(4)) return 4;
   if (d.ncs % 2 == 0 && enough(2)) return 2;
@@ -293,6 +255,8 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
   p.run_len = forward_run_len(d, static_cast<long long>(grid) * WARPS);
   p.interleave = p.run_len == d.ncs;
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
   BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_y, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
@@ -302,26 +266,13 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
 template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
 int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
   const bool ragged = d.L % (64 * NBOX) != 0;
-  if (precise_forward()) {
-    if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
-    return launch_forward_impl<COEF, OUT_F32, CKPT, true, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
-  }
-  if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, false, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
-  return launch_forward_impl<COEF, OUT_F32, CKPT, true, false, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  return launch_forward_impl<COEF, OUT_F32, CKPT, true, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
 }
 
+// Launch shape of the forward kernel: 128-token chunks (2 boxes), 3 stages, 4 warps per CTA (16 warps per SM).
 template <int COEF, bool OUT_F32, bool CKPT>
 int forward_variant(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t s) {
-  if constexpr (COEF == kCoefBf16 && !OUT_F32 && !CKPT) {  // the benchmarked path has tuning variants
-    switch (variant()) {
-      case 1: return launch_forward<COEF, OUT_F32, CKPT, 2, 4, 4>(coeff, x, y, ckpt, d, k, s);
-      case 2: return launch_forward<COEF, OUT_F32, CKPT, 1, 4, 4>(coeff, x, y, ckpt, d, k, s);
-      case 3: return launch_forward<COEF, OUT_F32, CKPT, 1, 3, 4>(coeff, x, y, ckpt, d, k, s);
-      case 4: return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 8>(coeff, x, y, ckpt, d, k, s);
-      case 5: return launch_forward<COEF, OUT_F32, CKPT, 1, 6, 4>(coeff, x, y, ckpt, d, k, s);
-      default: break;
-    }
-  }
   return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 4>(coeff, x, y, ckpt, d, k, s);
 }
 
@@ -358,6 +309,8 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
   p.coeff = coeff; p.x = x; p.dy = dy; p.dA = dA;
   p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = (k == 2);
   p.interleave = use_interleave(d, static_cast<long long>(grid) * WARPS);
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
   BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_dy, tm_dx, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
@@ -367,38 +320,17 @@ template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
 int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
                     cudaStream_t stream) {
   const bool ragged = d.L % (64 * NBOX) != 0;
-  if (precise_backward()) {
-    if (!ragged) return launch_backward_impl<COEF, DY_F32, false, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
-    return launch_backward_impl<COEF, DY_F32, true, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
-  }
-  if (!ragged) return launch_backward_impl<COEF, DY_F32, false, false, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
-  return launch_backward_impl<COEF, DY_F32, true, false, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  if (!ragged) return launch_backward_impl<COEF, DY_F32, false, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  return launch_backward_impl<COEF, DY_F32, true, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
 }
 
+// Launch shape of the backward kernel: 64-token chunks, 3 x-stages + 2 dy-stages, 4 warps per CTA.
 template <int COEF, bool DY_F32>
 int backward_variant(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k, cudaStream_t s) {
-  if constexpr (COEF == kCoefBf16 && !DY_F32) {
-    switch (variant()) {
-      case 1: return launch_backward<COEF, DY_F32, 1, 4, 4>(coeff, x, dy, dx, dA, d, k, s);
-      case 2: return launch_backward<COEF, DY_F32, 1, 3, 8>(coeff, x, dy, dx, dA, d, k, s);
-      case 3: return launch_backward<COEF, DY_F32, 1, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
-      case 4: return launch_backward<COEF, DY_F32, 2, 3, 2>(coeff, x, dy, dx, dA, d, k, s);
-      case 5: return launch_backward<COEF, DY_F32, 1, 4, 3>(coeff, x, dy, dx, dA, d, k, s);
-      default: break;
-    }
-  }
   return launch_backward<COEF, DY_F32, 1, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
 }
 
 // ------------------------------------------------------------------ gated forward launch
-int gated_forward_variant() {
-  static const int v = [] {
-    const char* e = getenv("BTP_SM100_GATED_VARIANT");
-    return e ? atoi(e) : 0;
-  }();
-  return v;
-}
-
 template <int TL, int STAGES>
 int launch_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out, int B, int L,
                          int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_out, int k,
@@ -544,13 +476,19 @@ int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, 
   if (!coeff || !x || !y) return fail(BTP_ERR_NULL_POINTER, "btp_sm100_forward_noalloc: coeff, x and y must not be NULL");
   if (misaligned(coeff) || misaligned(x) || misaligned(y))
     return fail(BTP_ERR_MISALIGNED, "btp_sm100_forward_noalloc: every pointer must be 16-byte aligned");
-  if (d.BH * L > static_cast<long long>(BTP_SM100_NOALLOC_MAX_HEAD_TOKENS))
+  // k == 1 has no carry and writes no record: the built-in array is not touched and its size does not matter
+  if (k == 2 && d.BH * L > static_cast<long long>(BTP_SM100_NOALLOC_MAX_HEAD_TOKENS))
     return fail(BTP_ERR_TOO_LARGE,
                 "btp_sm100_forward_noalloc: B*H*L = %lld exceeds the built-in scratch of %d head-tokens; "
                 "call btp_sm100_forward with a checkpoint buffer of your own",
                 d.BH * L, BTP_SM100_NOALLOC_MAX_HEAD_TOKENS);
+  {
+    int dev;
+    DeviceInfo info;
+    if ((rc = device_info(&dev, &info))) return rc;  // an unsupported device is reported as such, not as a failed lookup
+  }
   float* scratch = nullptr;
-  if ((rc = noalloc_scratch(&scratch))) return rc;
+  if (k == 2 && (rc = noalloc_scratch(&scratch))) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (coeff_dtype) {
     case BTP_DTYPE_BF16: return forward_coef<kCoefBf16>(coeff, x, y, scratch, d, k, out_dtype, s);
@@ -575,10 +513,6 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
     return fail(BTP_ERR_MISALIGNED, "%s: row pitches of B_logits, C, V and out must be multiples of 8 elements", fn);
   if (misaligned(b_logits) || misaligned(c) || misaligned(v) || misaligned(out) || (reinterpret_cast<uintptr_t>(a_logits) & 1u))
     return fail(BTP_ERR_MISALIGNED, "%s: B_logits, C, V and out must be 16-byte aligned", fn);
-  const int variant_id = gated_forward_variant();
-  if (variant_id == 1) return launch_gated_forward<32, 3>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
-  if (variant_id == 2) return launch_gated_forward<32, 4>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
-  if (variant_id == 3) return launch_gated_forward<64, 3>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
   // Measured on B200: 32-token chunks (6 CTAs per SM) are 5-7 % faster than 64-token chunks (3 CTAs per SM) as
   // long as whole sequences can still be dealt round-robin to the larger grid and the sequences are short;
   // with few or long sequences the 64-token kernel wins (by up to 28 % at L = 2048 with 2048 head groups).
@@ -721,6 +655,28 @@ int btp_sm100_prefill_state(const void* a, const void* x, void* h_loc, void* r_p
                                         : launch_prefill_state<__nv_bfloat16, float>(p, s);
   return gate_dtype == BTP_DTYPE_BF16 ? launch_prefill_state<float, __nv_bfloat16>(p, s) : launch_prefill_state<float, float>(p, s);
 }
+
+int btp_sm100_noalloc_read_record(float* dst, long long n_floats, void* stream) {
+  const char* fn = "btp_sm100_noalloc_read_record";
+  if (!dst) return fail(BTP_ERR_NULL_POINTER, "%s: dst must not be NULL", fn);
+  if (n_floats <= 0 || n_floats > static_cast<long long>(BTP_SM100_NOALLOC_MAX_HEAD_TOKENS))
+    return fail(BTP_ERR_BAD_SHAPE, "%s: n_floats must be in [1, %d] (got %lld)", fn, BTP_SM100_NOALLOC_MAX_HEAD_TOKENS, n_floats);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  float* scratch = nullptr;
+  if ((rc = noalloc_scratch(&scratch))) return rc;
+  BTP_CUDA_TRY(cudaMemcpyAsync(dst, scratch, static_cast<size_t>(n_floats) * sizeof(float), cudaMemcpyDeviceToDevice,
+                               static_cast<cudaStream_t>(stream)));
+  return BTP_OK;
+}
+
+unsigned long long btp_sm100_set_wait_limit(unsigned long long ns) {
+  return g_wait_limit_ns.exchange(ns ? ns : btp::kWaitLimitNs, std::memory_order_relaxed);
+}
+
+void btp_sm100_test_expect_missing_bytes(unsigned int bytes) { g_test_missing_tx.store(bytes, std::memory_order_relaxed); }
 
 const char* btp_sm100_status_string(int status) {
   switch (status) {

@@ -38,7 +38,20 @@ def _rows(t: torch.Tensor, cols: int, what: str) -> int:
     return t.stride(1)
 
 
+def _same_batch_and_length(a_logits: torch.Tensor, others) -> None:
+    """Every [B, L, .] tensor of one call must share a_logits' B, L and device: the kernels build their
+    descriptors over [B][L] from a_logits alone, so a shorter tensor would be read or written out of bounds."""
+    if a_logits.dim() != 3:
+        raise ValueError(f"a_logits must be [B, L, H], got {tuple(a_logits.shape)}")
+    for t, name in others:
+        if t.dim() != 3 or t.shape[:2] != a_logits.shape[:2]:
+            raise ValueError(f"{name} must share a_logits' batch and length {tuple(a_logits.shape[:2])}, got {tuple(t.shape)}")
+        if t.device != a_logits.device:
+            raise ValueError(f"{name} is on {t.device}, a_logits on {a_logits.device}")
+
+
 def _launch_forward(a_logits, b_logits, c, v, out, k: int) -> None:
+    _same_batch_and_length(a_logits, ((b_logits, "b_logits"), (c, "c"), (v, "v"), (out, "out")))
     B, L, H = a_logits.shape
     cols = H * 16
     ld_a = _rows(a_logits, H, "a_logits")
@@ -48,18 +61,6 @@ def _launch_forward(a_logits, b_logits, c, v, out, k: int) -> None:
         rc = _lib.load().btp_sm100_gated_forward(p(a_logits), p(b_logits), p(c), p(v), p(out), B, L, H, ld_a, ld_b, ld_c,
                                                  ld_v, ld_o, int(k), ctypes.c_void_p(stream))
     _lib.check(rc, "btp_sm100_gated_forward")
-
-
-def _to_heads(t: torch.Tensor, H: int) -> torch.Tensor:
-    """[B, L, H*16] -> contiguous [B, H, 16, L]"""
-    B, L, _ = t.shape
-    return t.reshape(B, L, H, 16).permute(0, 2, 3, 1).contiguous()
-
-
-def _to_tokens(t: torch.Tensor) -> torch.Tensor:
-    """[B, H, 16, L] -> [B, L, H*16]"""
-    B, H, D, L = t.shape
-    return t.permute(0, 3, 1, 2).reshape(B, L, H * D)
 
 
 class _GatedBTP(torch.autograd.Function):
@@ -74,15 +75,12 @@ class _GatedBTP(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         a_logits, b_logits, c, v = ctx.saved_tensors
-        if _FUSED_BACKWARD:
-            return _backward_fused(a_logits, b_logits, c, v, dout, ctx.k) + (None,)
-        return _backward_unfused(a_logits, b_logits, c, v, dout, ctx.k) + (None,)
-
-
-_FUSED_BACKWARD = True  # False: the op's own backward kernel between elementwise CUDA passes (for comparison)
+        return _backward(a_logits, b_logits, c, v, dout, ctx.k) + (None,)
 
 
 def _launch_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, k: int) -> None:
+    _same_batch_and_length(a_logits, ((b_logits, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"), (da, "da_logits"),
+                                      (db, "db_logits"), (dc, "dc"), (dv, "dv")))
     B, L, H = a_logits.shape
     cols = H * 16
     ld = [_rows(a_logits, H, "a_logits")] + [_rows(t, cols, n) for t, n in
@@ -128,7 +126,7 @@ _iface._register(_iface._LIB, "spear_btp", "gated_forward_wide", _op_gated_forwa
 _iface._register(_iface._LIB, "spear_btp", "gated_backward_wide", _op_gated_backward_wide, _fake, ["dwide"])
 
 
-def _backward_fused(a_logits, b_logits, c, v, dout, k):
+def _backward(a_logits, b_logits, c, v, dout, k):
     B, L, H = a_logits.shape
     cols = H * 16
     dout = dout if dout.stride(2) == 1 else dout.contiguous()
@@ -136,27 +134,6 @@ def _backward_fused(a_logits, b_logits, c, v, dout, k):
     db, dc, dv = (torch.empty(B, L, cols, device=v.device, dtype=v.dtype) for _ in range(3))
     torch.ops.spear_btp.gated_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, int(k))
     return da, db, dc, dv
-
-
-def _backward_unfused(a_logits, b_logits, c, v, dout, k):
-    B, L, H = a_logits.shape
-    a = torch.sigmoid(a_logits).transpose(1, 2).contiguous()
-    sb = torch.sigmoid(b_logits)
-    x = _to_heads(sb * v, H)
-    y = torch.empty_like(x)
-    _native.forward(a, x, y, None, k, 32)
-    dout = dout.contiguous()
-    dy = _to_heads(dout * c, H)
-    dx = torch.empty_like(x)
-    dA = torch.empty(a.shape, device=a.device, dtype=torch.float32)
-    _native.backward(a, x, dy, None, dx, dA, k, 32)
-    dx_t = _to_tokens(dx)
-    dc = dout * _to_tokens(y)
-    dv = dout + dx_t * sb
-    db = dx_t * v * (sb * (1 - sb))
-    af = a.float()
-    da_logits = (dA * af * (1 - af)).transpose(1, 2).to(a_logits.dtype)
-    return da_logits, db, dc, dv
 
 
 def _split_wide(wide: torch.Tensor, H: int):

@@ -67,8 +67,11 @@ def run_bwd(native, a, x, dy, *, k=2, dy_dtype=torch.bfloat16, coeff_dtype=torch
 
 
 def assert_limits(got, want, limits, what):
+    """Relative L2 <= 1e-2, and every absolute limit in `limits` (None: relative L2 only)."""
     m = O.error_metrics(got, want)
     assert m["rel_l2"] <= REL_L2, f"{what}: rel_l2 {m['rel_l2']:.3e}"
+    for key, limit in (limits or {}).items():
+        assert m[key] <= limit, f"{what}: {key} {m[key]:.3e} exceeds {limit:.3e}"
     return m
 
 
@@ -348,6 +351,44 @@ def test_full_size_properties(native, B, H, L):
     native.forward(a, (x.float() * 2).bfloat16(), y2, None, 2, 32)
     assert torch.equal(y2.float(), y.float() * 2)
     assert torch.isfinite(dA).all() and torch.isfinite(dx.float()).all()
+
+
+@pytest.mark.parametrize("log_coeff", [True, False])
+def test_long_sequences_with_near_unit_float32_decays_at_full_size(native, log_coeff):
+    """The long-sequence benchmark configuration as stated: B=16, H=64, L=8192 (512 blocks per sequence),
+    x ~ N(0, 1/16) bf16, dy ~ N(0, 1) bf16, decays log a ~ U(-1e-3, 0) given in float32 - as log a (the form the
+    configuration names) and as a.  bf16 cannot hold these decays (they all round to 1), so this is the
+    float32-coefficient entry; at this length the forward kernel deals runs of four chunks round-robin, each run
+    recomputing its incoming carry.  Forward and backward on the whole tensor; a sample of whole sequences
+    (first, last and two in between, every head) against the float64 oracle: relative L2 <= 1e-2 for y and dx,
+    and dA at float32 accuracy."""
+    B, H, L = 16, 64, 8192
+    gen = torch.Generator(device="cuda").manual_seed(8192)
+    loga = -1e-3 * torch.rand(B, H, L, device="cuda", generator=gen)
+    a = torch.exp(loga)
+    x = (torch.randn(B, H, 16, L, device="cuda", generator=gen) * 0.25).bfloat16()
+    dy = torch.randn(B, H, 16, L, device="cuda", generator=gen).bfloat16()
+    coeff = loga if log_coeff else a
+    y = torch.full_like(x, float("nan"))
+    dx = torch.full_like(x, float("nan"))
+    dA = torch.full((B, H, L), float("nan"), device="cuda")
+    native.forward(coeff, x, y, None, 2, 32, log_coeff=log_coeff)
+    native.backward(coeff, x, dy, None, dx, dA, 2, 32, log_coeff=log_coeff)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all() and torch.isfinite(dx.float()).all() and torch.isfinite(dA).all()
+    idx = torch.tensor([0, 5, 10, B - 1])
+    # the oracle sees exactly the decay the kernel was given: exp(log a) in float64 for the log entry, a otherwise
+    a_s = torch.exp(loga[idx].double().cpu()) if log_coeff else a[idx].double().cpu()
+    x_s, dy_s = x[idx].double().cpu(), dy[idx].double().cpu()
+    y_w = O.btp_forward(a_s, x_s)
+    dA_w, dx_w = O.btp_backward(a_s, x_s, dy_s)
+    if log_coeff:
+        dA_w = dA_w * a_s  # gradient with respect to log a
+    assert_limits(y[idx].float().cpu(), y_w.float(), FORWARD_LIMITS, "y")
+    assert_limits(dx[idx].float().cpu(), dx_w.float(), BACKWARD_LIMITS, "dx")
+    assert_limits(dA[idx].cpu(), dA_w.float(), None, "dA")
+    rel = O.rel_l2(dA[idx].double().cpu(), dA_w)
+    assert rel <= 5e-6, f"dA rel_l2 against float64 {rel:.3e}"
 
 
 # ------------------------------------------------------------------ argument checking at the boundary
@@ -775,11 +816,11 @@ def test_tensors_beyond_4_gib(native):
         want = _gated_oracle(al[b:b + 1].cpu(), bl[b:b + 1].cpu(), c[b:b + 1].cpu(), v[b:b + 1].cpu())
         assert O.rel_l2(out[b:b + 1].float().cpu(), want) <= 1e-2, f"gated out, batch entry {b}"
     # gated backward on the full tensors against the same kernel on single batch entries
-    from spear_b200.ops.btp.gated import _backward_fused
+    from spear_b200.ops.btp.gated import _backward
     del out
-    full = _backward_fused(al, bl, c, v, bl, 2)
+    full = _backward(al, bl, c, v, bl, 2)
     for b in (0, 2048, 2303):
-        part = _backward_fused(al[b:b + 1], bl[b:b + 1], c[b:b + 1], v[b:b + 1], bl[b:b + 1], 2)
+        part = _backward(al[b:b + 1], bl[b:b + 1], c[b:b + 1], v[b:b + 1], bl[b:b + 1], 2)
         for f, q, name in zip(full, part, ("da_logits", "db_logits", "dc", "dv")):
             assert O.rel_l2(f[b:b + 1].float().cpu(), q.float().cpu()) <= 2e-3, f"gated {name}, batch entry {b}"
 

@@ -40,7 +40,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_status_strings(lib):
-    assert lib.btp_sm100_abi_version() == 1
+    assert lib.btp_sm100_abi_version() == 2
     seen = set()
     for code in range(0, -10, -1):
         name = lib.btp_sm100_status_string(code).decode()
@@ -160,3 +160,31 @@ def test_python_wrapper_has_no_cpu_path():
         Phalanx(dim=64, heads=2)   # head_dim must be 16 (swr.py:247-249)
     with pytest.raises(ValueError):
         Phalanx(dim=64, kv_heads=3)
+
+
+def test_gated_wrappers_refuse_mismatched_shapes_before_any_launch():
+    """The gated kernels size their descriptors from a_logits alone; a tensor with fewer tokens or batch entries
+    must be refused on the host (ValueError), never reach a launch."""
+    import torch
+
+    from spear_b200 import _lib
+    from spear_b200.ops.btp import gated
+
+    B, L, H = 2, 32, 4
+    mk = lambda b, l, c: torch.zeros(b, l, c, dtype=torch.bfloat16)
+    al, bl, c, v, out = mk(B, L, H), mk(B, L, 64), mk(B, L, 64), mk(B, L, 64), mk(B, L, 64)
+    before = _lib.launch_count() if os.path.exists(_lib.LIB_PATH) else 0
+    for bad in (dict(v=mk(B, L - 16, 64)), dict(c=mk(B - 1, L, 64)), dict(out=mk(B, L // 2, 64)), dict(bl=mk(B, 2 * L, 64))):
+        args = {**dict(al=al, bl=bl, c=c, v=v, out=out), **bad}
+        with pytest.raises(ValueError, match="batch and length"):
+            gated._launch_forward(args["al"], args["bl"], args["c"], args["v"], args["out"], 2)
+    grads = [mk(B, L, H)] + [mk(B, L, 64) for _ in range(3)]
+    for i in range(4):
+        g = list(grads)
+        g[i] = mk(B, L + 16, g[i].shape[2])
+        with pytest.raises(ValueError, match="batch and length"):
+            gated._launch_backward(al, bl, c, v, out, *g, 2)
+    with pytest.raises(ValueError, match="batch and length"):
+        gated._launch_backward(al, bl, c, v, mk(B, L - 16, 64), *grads, 2)
+    if os.path.exists(_lib.LIB_PATH):
+        assert _lib.launch_count() == before

@@ -1,6 +1,7 @@
 """With `spear_b200.install_as_spear_backend()`, the UNMODIFIED reference package imports and its
-wrapper reaches this package's binding.  Needs the reference checkout, which exists only in the build
-container: skipped elsewhere.  Runs in a child process because both packages define the `spear_btp` ops."""
+wrapper reaches this package's binding.  Uses the copy of the reference that oracle/stage_reference.py staged
+under oracle/_ref (or the checkout SPEAR_REFERENCE names); skipped where neither exists.  Runs in a child
+process because both packages define the `spear_btp` ops."""
 
 from __future__ import annotations
 
@@ -12,7 +13,7 @@ import pytest
 
 from conftest import ROOT
 
-REFERENCE = os.environ.get("SPEAR_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("SPEAR_REFERENCE") or os.path.join(ROOT, "oracle", "_ref")
 
 CHILD = r"""
 import sys, inspect

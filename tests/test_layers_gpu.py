@@ -61,20 +61,22 @@ LAYER_FORWARD_LIMITS = {"max_abs": 1e-1, "mean_abs": 1e-2, "rmse": 5e-2}      # 
 LAYER_BACKWARD_LIMITS = {"max_abs": 2.2, "mean_abs": 2.2e-1, "rmse": 5e-1}    # test_phalanx_numerics.py:49-55
 
 
-def _layer_and_oracle(B, L, dim, stress, layer_seed, input_seed, kv_heads=None):
+def _layer_and_oracle(B, L, dim, stress, layer_seed, input_seed, kv_heads=None, prepare=None, decay_dtype=None):
     """bf16 layer on the kernels next to the float32 CPU oracle of the same data flow with the same (bf16) weights,
-    forward and autograd backward."""
+    forward and autograd backward.  `prepare(layer)` may edit the weights first."""
     import btp_oracle as O
     from spear_b200.nn.phalanx import Phalanx
 
     torch.manual_seed(layer_seed)
     layer = Phalanx(dim=dim, length=L, dtype=torch.bfloat16, kv_heads=kv_heads).cuda()
+    if prepare is not None:
+        prepare(layer)
     g = torch.Generator().manual_seed(input_seed)
     u = (torch.randn(B, L, dim, generator=g) * stress).bfloat16()
     dout = torch.randn(B, L, dim, generator=g).bfloat16()
     state = {k: v.float().cpu().requires_grad_(True) for k, v in layer.state_dict().items()}
     u_ref = u.float().requires_grad_(True)
-    want = O.phalanx_forward(state, u_ref, kv_heads=kv_heads)
+    want = O.phalanx_forward(state, u_ref, kv_heads=kv_heads, decay_dtype=decay_dtype)
     want.backward(dout.float())
     ud = u.cuda().requires_grad_(True)
     out = layer(ud)
@@ -119,3 +121,32 @@ def test_layer_kv_grouping(kv_heads_divisor):
     _check(out, want, LAYER_FORWARD_LIMITS, f"out kv_heads={kv_heads}")
     _check(du, du_want, LAYER_BACKWARD_LIMITS, "du")
     _check_param_grads(layer, state)
+
+
+def test_layer_at_the_sharded_benchmark_shape_and_decay_mix():
+    """The shape of the sharded layer benchmark: dim 2048 (128 heads), L 2048, with the decays fixed through
+    proj_a.bias so that half the heads have log a ~ U(-1e-3, 0) and half U(-4, -1); batch 2 (one rank's slice of
+    the global batch is 8 at eight GPUs; the batch entries are independent).  Fused path (one wide projection,
+    gated kernels) against the float32 oracle of the layer's data flow with the layer's bf16 decays; forward,
+    input gradient and every parameter gradient.  Relative bounds: at this width the outputs are sums over
+    2048 inputs and the reference's absolute limits, set at dim 256, do not apply."""
+    import btp_oracle as O
+    from bench_layer import set_decay_mix
+
+    B, L, dim = 2, 2048, 2048
+    layer, state, (out, want), (du, du_want) = _layer_and_oracle(B, L, dim, 1.0, 2048, 4096, prepare=set_decay_mix,
+                                                                 decay_dtype=torch.bfloat16)
+    assert layer.fused_gating and layer.fused_projection
+    a = torch.sigmoid(layer.param.proj_a.bias.float())
+    assert (a[: dim // 32] > 0.99).all() and (a[dim // 32:] < 0.4).all()  # both halves of the mix are present
+    rel = O.rel_l2(out.float().cpu(), want.detach())
+    assert rel <= 3e-2, f"out rel_l2 {rel:.3e}"
+    rel = O.rel_l2(du.float().cpu(), du_want)
+    assert rel <= 5e-2, f"du rel_l2 {rel:.3e}"
+    for name, p in layer.named_parameters():
+        if name == "param.proj_a.weight":
+            continue  # checked below: with a zero weight the oracle's gradient is tiny and both are mostly rounding
+        rel = O.rel_l2(p.grad.float().cpu(), state[name].grad)
+        assert rel <= 6e-2, f"grad {name}: rel_l2 {rel:.3e}"
+    ga, gw = layer.param.proj_a.weight.grad.float().cpu(), state["param.proj_a.weight"].grad
+    assert O.rel_l2(ga, gw) <= 1.5e-1, f"grad proj_a.weight rel_l2 {O.rel_l2(ga, gw):.3e}"

@@ -115,7 +115,16 @@ def test_one_process_driving_two_devices():
         y = torch.empty_like(xd)
         rc = lib.btp_sm100_forward_noalloc(p(ad), p(xd), p(y), B, H, L, 2, 0, 0, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
         assert rc == 0, lib.btp_sm100_last_error().decode()
+        # the record went to THIS device's copy of the array: it equals the checkpoint of the ordinary entry point
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        nb = L // 16
+        ckpt = torch.empty(B, H, nb, 16, device=dev, dtype=torch.float32)
+        y2 = torch.empty_like(xd)
+        assert lib.btp_sm100_forward(p(ad), p(xd), p(y2), p(ckpt), B, H, L, 2, 0, 0, stream) == 0
+        record = torch.full((B, H, nb, 16), float("nan"), device=dev, dtype=torch.float32)
+        assert lib.btp_sm100_noalloc_read_record(p(record), record.numel(), stream) == 0
         torch.cuda.synchronize(dev)
+        assert torch.equal(record[:, :, : nb - 1], ckpt[:, :, : nb - 1])
         ys.append(y.cpu())
     assert torch.equal(ys[0], ys[1]) and O.rel_l2(ys[0].float(), y_w) <= 1e-2
     # a layer on the second device while the first one is current
