@@ -204,9 +204,11 @@ def phalanx_forward(state: dict, u: torch.Tensor, k: int = 2, kv_heads: int | No
     """The Phalanx layer's data flow around the oracle op, in the dtype of `u` on CPU.
 
     `decay_dtype`: the reference layer computes its projections and the sigmoid in bfloat16
-    (spear/nn/phalanx/swr.py:146,170,216), so the decay it hands to the op is a bfloat16 number.  Decays close
-    to one (0.9995) do not survive that rounding; passing torch.bfloat16 here rounds A the same way (gradients
-    pass straight through the rounding), so that a higher-precision evaluation still sees the layer's decays.
+    (spear/nn/phalanx/swr.py:146,170,216): the logits of the decay are bfloat16 numbers, the decay it hands to
+    the op is one, and autograd differentiates the sigmoid at that rounded value, a(1 - a).  Decays close to one
+    (0.9995) do not survive the rounding.  Passing torch.bfloat16 here runs exactly that pair of operations -
+    cast the logits, sigmoid in that dtype - in the middle of an otherwise higher-precision evaluation, so that
+    the oracle sees the layer's decays and their gradients (zero where the decay rounds to one).
 
     Follows spear/nn/phalanx/swr.py:157-175 (the four projections), :96-103 (head h reads key/value head
     h // (heads / kv_heads)), :196-221 (A = sigmoid, X = sigmoid(B) * V), :311-327 (y * C + V, output
@@ -221,9 +223,11 @@ def phalanx_forward(state: dict, u: torch.Tensor, k: int = 2, kv_heads: int | No
     KV = H if kv_heads is None else kv_heads
     idx = torch.arange(H) // (H // KV)
     heads = lambda t, n: t.transpose(1, 2).reshape(Bsz, n, D, L)
-    A = torch.sigmoid(lin("proj_a", u)).transpose(1, 2)
+    a_logits = lin("proj_a", u)
     if decay_dtype is not None:
-        A = A + (A.to(decay_dtype).to(A.dtype) - A).detach()
+        A = torch.sigmoid(a_logits.to(decay_dtype)).to(u.dtype).transpose(1, 2)
+    else:
+        A = torch.sigmoid(a_logits).transpose(1, 2)
     Bg = heads(lin("proj_b", u), KV).index_select(1, idx)
     C = heads(lin("proj_c", u), KV).index_select(1, idx)
     V = heads(lin("proj_v", u), H)

@@ -379,9 +379,11 @@ __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* c
     const float2 a1 = *reinterpret_cast<const float2*>(p + row_g + 8 + 2 * t);
     const float2 b0 = *reinterpret_cast<const float2*>(p + row_g8 + 2 * t);
     const float2 b1 = *reinterpret_cast<const float2*>(p + row_g8 + 8 + 2 * t);
-    // the tensor-core path feeds dy rounded to bf16
-    e[0][0] = round_bf16(a0.x); e[0][1] = round_bf16(a0.y); e[0][2] = round_bf16(a1.x); e[0][3] = round_bf16(a1.y);
-    e[1][0] = round_bf16(b0.x); e[1][1] = round_bf16(b0.y); e[1][2] = round_bf16(b1.x); e[1][3] = round_bf16(b1.y);
+    // what the tensor-core path feeds: dy as one bf16 term, or as two (hi + lo) when PRECISE
+    e[0][0] = lmat_weight<PRECISE>(a0.x); e[0][1] = lmat_weight<PRECISE>(a0.y);
+    e[0][2] = lmat_weight<PRECISE>(a1.x); e[0][3] = lmat_weight<PRECISE>(a1.y);
+    e[1][0] = lmat_weight<PRECISE>(b0.x); e[1][1] = lmat_weight<PRECISE>(b0.y);
+    e[1][2] = lmat_weight<PRECISE>(b1.x); e[1][3] = lmat_weight<PRECISE>(b1.y);
   } else {
     const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(tile_base);
     const uint32_t a0 = *reinterpret_cast<const uint32_t*>(p + row_g + 2 * t);
@@ -787,6 +789,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const uint32_t g10 = movmatrix_trans(lf.b10);
     const uint32_t g11 = movmatrix_trans(lf.b11);
     uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+    uint32_t l0 = 0, l1 = 0, l2 = 0, l3 = 0;  // second bf16 term of a float32 dy
     ldmatrix_x4(ldm_x + box * 2048 + tl.ldm_off[ib], a0, a1, a2, a3);
     if constexpr (DY_F32) {
       // [16][32] float boxes, 128-byte swizzle: block i sits in box i/2 at byte offset (i&1)*64 of each row
@@ -798,11 +801,16 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(r.x), "=f"(r.y) : "r"(addr));
         return r;
       };
-      float2 f;
-      f = lds(bb + ((c_lo ^ tl.g) << 4) + in);         e0 = pack_bf16x2(f.x, f.y);
-      f = lds(bb + 1024 + ((c_lo ^ tl.g) << 4) + in);  e1 = pack_bf16x2(f.x, f.y);
-      f = lds(bb + ((c_hi ^ tl.g) << 4) + in);         e2 = pack_bf16x2(f.x, f.y);
-      f = lds(bb + 1024 + ((c_hi ^ tl.g) << 4) + in);  e3 = pack_bf16x2(f.x, f.y);
+      // A float32 dy goes to the tensor cores as two bf16 terms as well (hi + lo), so that dA keeps float32
+      // accuracy for float32 upstream gradients (the op's default output type makes them float32).
+      auto split = [&](const float2 f, uint32_t& hi, uint32_t& lo) {
+        hi = pack_bf16x2(f.x, f.y);
+        if constexpr (PRECISE) lo = pack_bf16x2(f.x - bf16_lo(hi), f.y - bf16_hi(hi));
+      };
+      split(lds(bb + ((c_lo ^ tl.g) << 4) + in), e0, l0);
+      split(lds(bb + 1024 + ((c_lo ^ tl.g) << 4) + in), e1, l1);
+      split(lds(bb + ((c_hi ^ tl.g) << 4) + in), e2, l2);
+      split(lds(bb + 1024 + ((c_hi ^ tl.g) << 4) + in), e3, l3);
     } else {
       ldmatrix_x4(dy_s + tl.ldm_base + box * 2048 + tl.ldm_off[ib], e0, e1, e2, e3);
     }
@@ -815,6 +823,10 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       mma_16816_acc(acc.v1, a0, a1, a2, a3, lo.b10, lo.b11);
       mma_16816_acc(acc.g0, e0, e1, e2, e3, movmatrix_trans(lo.b00), movmatrix_trans(lo.b10));
       mma_1688_acc(acc.g1, e2, e3, movmatrix_trans(lo.b11));
+      if constexpr (DY_F32) {  // dy_lo . Lmat_hi (the lo . lo term is below float32 resolution)
+        mma_16816_acc(acc.g0, l0, l1, l2, l3, g00, g10);
+        mma_1688_acc(acc.g1, l2, l3, g11);
+      }
     }
     // gradient this block sends to its left neighbour: P[0] * gw[:,0]   (P[0] = Pshift[1])
     const float a_first = tab[TL + 16 * i + 1];

@@ -201,8 +201,9 @@ __device__ __forceinline__ float rcp_approx(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// logistic function through one tanh (absolute error of a few 1e-4, below bf16 resolution near 1)
-__device__ __forceinline__ float sigmoid_fast(float z) { return fmaf(tanh_approx(0.5f * z), 0.5f, 0.5f); }
+// logistic function 1 / (1 + 2^(-z log2 e)): relative error of a few 2^-22 over the whole range, so that
+// saturated gates (sigma ~ 1e-4) keep their relative accuracy; exactly 0 and 1 at the far ends.
+__device__ __forceinline__ float sigmoid_fast(float z) { return rcp_approx(1.0f + ex2(z * -1.4426950408889634f)); }
 // lo -> bits 0..15, hi -> bits 16..31, round to nearest even.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t d;

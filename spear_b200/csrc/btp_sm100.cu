@@ -57,8 +57,44 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// [rows = BH*16][cols = L] tensor, box = 16 rows x `box_cols` (one 128-byte swizzle span).
+// Encoded descriptors, remembered per calling thread: a descriptor depends only on (base address, element type,
+// rows, L), a training loop presents the same few tensors again and again, and encoding one costs about a
+// microsecond of host time - as much as the rest of a call.  Thread-local, so no lock; 16 entries, replaced
+// round-robin.  (A descriptor holds no device state: reusing one for a buffer that was freed and allocated
+// again at the same address with the same shape is correct.)
+struct MapCacheEntry {
+  const void* base = nullptr;
+  long long rows = 0;
+  int L = 0;
+  int kind = -1;  // 0: bf16 rows of x/y/dy/dx, 1: float rows of dy
+  CUtensorMap map;
+};
+struct MapCache {
+  MapCacheEntry e[16];
+  unsigned next = 0;
+};
+thread_local MapCache tls_maps;
+
+int encode_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L);
+
+// [rows = BH*16][cols = L] tensor, box = 16 rows x one 128-byte swizzle span.
 int make_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L) {
+  MapCache& c = tls_maps;
+  const int kind = f32 ? 1 : 0;
+  for (const MapCacheEntry& e : c.e) {
+    if (e.base == base && e.rows == rows && e.L == L && e.kind == kind) {
+      *map = e.map;
+      return BTP_OK;
+    }
+  }
+  const int rc = encode_map(map, base, f32, rows, L);
+  if (rc) return rc;
+  MapCacheEntry& slot = c.e[c.next++ & 15u];
+  slot.base = base; slot.rows = rows; slot.L = L; slot.kind = kind; slot.map = *map;
+  return BTP_OK;
+}
+
+int encode_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint32_t esz = f32 ? 4 : 2;
@@ -104,15 +140,22 @@ int device_info(int* dev_out, DeviceInfo* info) {
   if (dev < 0 || dev >= 64) return fail(BTP_ERR_CUDA, "device ordinal %d out of range", dev);
   // Binds the device's primary context to the calling thread: the descriptor encoder is a driver entry point
   // and threads that have made no runtime call yet (autograd's backward thread) have no current context.
-  BTP_CUDA_TRY(cudaSetDevice(dev));
-  std::lock_guard<std::mutex> lock(g_dev_mutex);
-  if (!g_dev[dev].ready) {
-    BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].sms, cudaDevAttrMultiProcessorCount, dev));
-    BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev));
-    g_dev[dev].ready = true;
+  // Once per thread and device; later calls find the binding in place.
+  thread_local int tls_bound_device = -1;
+  thread_local DeviceInfo tls_info;
+  if (tls_bound_device != dev) {
+    BTP_CUDA_TRY(cudaSetDevice(dev));
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (!g_dev[dev].ready) {
+      BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+      BTP_CUDA_TRY(cudaDeviceGetAttribute(&g_dev[dev].cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+      g_dev[dev].ready = true;
+    }
+    tls_info = g_dev[dev];
+    tls_bound_device = dev;
   }
   *dev_out = dev;
-  *info = g_dev[dev];
+  *info = tls_info;
   if (info->cc_major != 10) {
     return fail(BTP_ERR_UNSUPPORTED_DEVICE, "device %d has compute capability %d.x; this library is built for 10.x only",
                 dev, info->cc_major);

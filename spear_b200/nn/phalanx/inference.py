@@ -67,6 +67,9 @@ def parallel_jagged(A, X, C, V, *, block_len: int, use_log_a: bool = False):
 
     A: (B,H,L) gates (log gates if use_log_a), X: (B,H,D,L) driving term, C, V: (B,H,D,L).
     Any L >= 1: the prompt is padded to a multiple of 16 with neutral tokens exactly as the reference pads it.
+    bf16 prompts take one launch of the forward kernel; wider prompts take two (see below) and keep their accuracy.
+    A kernel wait that gives up leaves its part of Y unwritten and is reported by `_lib.device_status()`: poll it
+    at a synchronisation point the caller already has (once per request or per step).
     """
     if block_len != BLOCK:
         raise NotImplementedError(f"the kernel's block length is {BLOCK} (got block_len={block_len})")
@@ -81,15 +84,24 @@ def parallel_jagged(A, X, C, V, *, block_len: int, use_log_a: bool = False):
     # The kernel takes bf16 x and bf16 / float32 gates (float32 log gates); tensors already in that form are
     # passed as they are, without a copy.
     coeff = A.float() if (use_log_a or A.dtype not in _KERNEL_DTYPES) else A
-    x = X if X.dtype == torch.bfloat16 else X.to(torch.bfloat16)
+    # A prompt wider than bf16 (float32, float16) is fed as TWO bf16 terms, X = hi + lo: the op is linear in x, so
+    # btp(a, hi) + btp(a, lo) is the result for X itself to about 2^-17, at the price of a second launch.  Y then
+    # has the accuracy of the input type, as in the reference, and agrees with the hand-off state below, which
+    # is computed from the unrounded X.
+    terms = [X if X.dtype == torch.bfloat16 else X.to(torch.bfloat16)]
+    if X.dtype != torch.bfloat16:
+        terms.append((X.float() - terms[0].float()).to(torch.bfloat16))
     if pad:
         coeff = torch.nn.functional.pad(coeff, (0, pad), value=0.0 if use_log_a else 1.0)
-        x = torch.nn.functional.pad(x, (0, pad), value=0.0)
+        terms = [torch.nn.functional.pad(t, (0, pad), value=0.0) for t in terms]
     coeff = coeff.contiguous()
-    x = x.contiguous()
-    low = V.dtype == torch.bfloat16 and C.dtype == torch.bfloat16
-    y = torch.empty(x.shape, device=x.device, dtype=torch.bfloat16 if low else torch.float32)
-    _native.forward(coeff, x, y, None, 2, 32, log_coeff=use_log_a)
+    low = len(terms) == 1 and V.dtype == torch.bfloat16 and C.dtype == torch.bfloat16
+    y = None
+    for t in terms:
+        t = t.contiguous()
+        yt = torch.empty(t.shape, device=t.device, dtype=torch.bfloat16 if low else torch.float32)
+        _native.forward(coeff, t, yt, None, 2, 32, log_coeff=use_log_a)
+        y = yt if y is None else y.add_(yt)
     y = y[..., :L] if pad else y
     if low:
         Y = torch.addcmul(V, y, C)  # one pass, fp32 arithmetic inside, one rounding

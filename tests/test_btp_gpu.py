@@ -158,6 +158,22 @@ def test_dA_keeps_float32_accuracy_with_and_without_seams(native, B, H, L):
     assert rel <= 5e-6, f"dA rel_l2 {rel:.3e}"
 
 
+@pytest.mark.parametrize("B,H,L", [(1, 2, 4096), (2, 8, 512), (64, 32, 128)])
+def test_dA_keeps_float32_accuracy_for_float32_upstream_gradients(native, B, H, L):
+    """The op's default output type is float32, so autograd hands the backward a float32 dy whose values bf16
+    cannot hold.  The reference kernel forms dA from that dy in float32 scalar code (btp-backwards.cu:355-413);
+    here dy goes to the tensor cores as two bf16 terms, which has to leave dA at the same accuracy as for a
+    bf16 dy.  (Rounded to one bf16 term, dA was off by 2^-9 and the reference's own gradient test
+    tests/btp/test_numerics.py:143-166 failed on sums of cancelling bf16 gradients.)"""
+    a, x, _ = sample(B, H, L, 19, 1.0)
+    dy = torch.randn(B, H, 16, L, generator=torch.Generator().manual_seed(20))  # not bf16-representable
+    dA_w, dx_w = O.btp_backward(a.double(), x.double(), dy.double())
+    dA, dx = run_bwd(native, a, x, dy, dy_dtype=torch.float32)
+    rel = O.rel_l2(dA.double(), dA_w)
+    assert rel <= 5e-6, f"dA rel_l2 {rel:.3e}"
+    assert_limits(dx, dx_w.float(), BACKWARD_LIMITS, "dx")
+
+
 def test_layer_parametrised_inputs_at_the_length_the_reference_kernel_fails(native):
     """B=1, H=16, L=8192 with A and X produced by the layer's own projections (dim 256, layer seed 987, input
     seed 789): the case the reference documents as failing for its CUDA backward, grad_coeff max_abs about 11
@@ -546,6 +562,53 @@ def test_gated_forward_vs_oracle(native, B, L, H, sliced):
         assert out.shape == want.shape and torch.isfinite(out.float()).all()
         m = O.error_metrics(out.float().cpu(), want)
         assert m["rel_l2"] <= 1e-2, f"gated out k={k}: rel_l2 {m['rel_l2']:.3e}"
+
+
+@pytest.mark.parametrize("lo,hi", [(-10.0, -4.0), (4.0, 10.0)])
+def test_gated_kernels_with_saturated_gates(native, lo, hi):
+    """B_logits far from zero: sigma = sigmoid(B_logits) is ~1e-4 ... 2e-2 (or 1 minus that).  The output part
+    that sigma drives (out - V, i.e. btp(a, sigma V) C) and dB_logits = dx V sigma (1 - sigma) are then tiny
+    numbers whose RELATIVE accuracy depends on the sigmoid's; the layer's torch.sigmoid in bf16 is good to 0.4 %.
+    Compared elementwise against the float32 oracle with a bf16-sized relative tolerance."""
+    from spear_b200.ops.btp.gated import gated_btp
+
+    B, L, H = 2, 64, 4
+    cols = H * 16
+    g = torch.Generator().manual_seed(77)
+    al = torch.randn(B, L, H, generator=g).bfloat16()
+    bl = (lo + (hi - lo) * torch.rand(B, L, cols, generator=g)).bfloat16()
+    c, v = (torch.randn(B, L, cols, generator=g).bfloat16() for _ in range(2))
+    dout = torch.randn(B, L, cols, generator=g).bfloat16()
+    ins = [t.cuda().requires_grad_(True) for t in (al, bl, c, v)]
+    out = gated_btp(*ins, 2)
+    out.backward(dout.cuda())
+    ref = [t.float().requires_grad_(True) for t in (al, bl, c, v)]
+    a = torch.sigmoid(ref[0].bfloat16()).float().transpose(1, 2)
+    heads = lambda t: t.reshape(B, L, H, 16).permute(0, 2, 3, 1)
+    # sigma as the layer forms it: torch.sigmoid on the bf16 logits, whose autograd differentiates at the ROUNDED
+    # value, sigma (1 - sigma) with sigma in bf16 (swr.py:217); near saturation that is a coarse number (0 where
+    # sigma rounds to 1) and it is the reference's gradient
+    x = torch.sigmoid(heads(ref[1]).bfloat16()).float() * heads(ref[3])
+    y = O.btp_forward(a.contiguous(), x.contiguous(), 2)
+    want = (y * heads(ref[2]) + heads(ref[3])).permute(0, 3, 1, 2).reshape(B, L, cols)
+    want.backward(dout.float())
+    # the sigma-driven part of the output, in float32 from the bf16 result: |out| ~ |v| ~ 1, so the bf16 rounding
+    # of `out` (2^-9) is the floor for what can be seen of a part of size ~1e-2; compare in relative L2
+    part, part_w = out.detach().float().cpu() - v.float(), want.detach() - v.float()
+    if hi < 0:
+        assert part_w.abs().max() < 0.5  # the gate really is nearly closed
+    db, db_w = ins[1].grad.float().cpu(), ref[1].grad
+    rel = O.rel_l2(db, db_w)
+    assert rel <= 1e-2, f"dB_logits rel_l2 {rel:.3e}"
+    # elementwise: bf16 rounding of the result (2^-8 relative) plus the bf16 roundings of sigma and x inside
+    if hi < 0:
+        big = db_w.abs() > db_w.abs().mean()
+        worst = ((db - db_w).abs() / db_w.abs())[big].max().item()
+        assert worst <= 5e-2, f"dB_logits worst relative error {worst:.3e}"
+    assert O.rel_l2(ins[3].grad.float().cpu(), ref[3].grad) <= 1e-2
+    assert O.rel_l2(ins[2].grad.float().cpu(), ref[2].grad) <= 1e-2
+    if lo > 0:
+        assert O.rel_l2(part, part_w) <= 1e-2
 
 
 def test_gated_backward_matches_unfused_layer(native):

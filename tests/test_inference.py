@@ -74,9 +74,16 @@ def test_prefill_on_the_kernel_then_decode(L):
     A, X, C, V = (dev(c[k]) for k in "AXCV")
     n0 = _lib.launch_count()
     Y, st = parallel_jagged(A[..., :L], X[..., :L], C[..., :L], V[..., :L], block_len=16)
-    assert _lib.launch_count() - n0 == 2  # forward kernel + state kernel
+    # the fixture's prompt is float32: two launches of the forward kernel (X as two bf16 terms) + the state kernel
+    assert A.dtype == torch.float32 and _lib.launch_count() - n0 == 3
     rel = lambda got, want: ((got.float().cpu() - want).norm() / want.norm()).item()
-    assert Y.shape == c["Y"].shape and rel(Y, c["Y"]) <= 1e-2
+    # Y at the accuracy of a float32 evaluation (the reference computes Y in the input type, inference.py:269-360)
+    assert Y.shape == c["Y"].shape and rel(Y, c["Y"]) <= 2e-5
+    assert torch.allclose(Y.cpu(), c["Y"], rtol=1e-4, atol=1e-4)
+    # the same prompt in bf16: one launch of the forward kernel, bf16 accuracy
+    n0 = _lib.launch_count()
+    Yb, _ = parallel_jagged(*(t[..., :L].bfloat16() for t in (A, X, C, V)), block_len=16)
+    assert _lib.launch_count() - n0 == 2 and Yb.dtype == torch.bfloat16 and rel(Yb, c["Y"]) <= 2e-2
     assert st.i == int(c["i"]) and st.block_len == 16
     assert torch.allclose(st.h_loc.cpu(), c["h_loc"], rtol=1e-5, atol=1e-5)
     assert torch.allclose(st.r_pref.cpu(), c["r_pref"], rtol=1e-5, atol=1e-6)
@@ -93,7 +100,7 @@ def test_prefill_on_the_kernel_then_decode(L):
     assert torch.allclose(y_again.cpu(), c["Ydec"][..., 0], rtol=1e-5, atol=1e-5)
     # log-gate prompt through the kernel's log-coefficient entry, then log-space decode
     Y2, st2 = parallel_jagged(torch.log(A[..., :L]), X[..., :L], C[..., :L], V[..., :L], block_len=16, use_log_a=True)
-    assert rel(Y2, c["Y"]) <= 1e-2
+    assert rel(Y2, c["Y"]) <= 2e-5
     assert torch.allclose(st2.r_pref.cpu(), c["r_pref"], rtol=1e-4, atol=1e-6)
     st2.use_log_r, st2.log_r_pref, st2.r_pref = True, torch.log(st2.r_pref), None
     for j in range(c["Ydec"].shape[-1]):
@@ -124,7 +131,7 @@ def test_streaming_kernels_against_oracle(L, dtype):
     Ad, Xd, Cd, Vd = (t.cuda() for t in (A, X, C, V))
     Y, st = parallel_jagged(Ad[..., :L], Xd[..., :L], Cd[..., :L], Vd[..., :L], block_len=16)
     assert Y.dtype == dtype and st.h_loc.dtype == dtype and st.r_pref.dtype == dtype
-    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-2, atol=1e-2)  # prompt runs in bf16
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)
     assert torch.allclose(Y.float().cpu(), Yo, **tol)
     stol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
     assert st.i == so.i
