@@ -136,6 +136,34 @@ __device__ __forceinline__ WarpSmem<LAYOUT, STAGES> carve_smem(unsigned char* ra
   return w;
 }
 
+// One lane's share of a chunk's asynchronous copies.  The copies of a chunk (its x boxes, its dy boxes, its row of
+// coefficients; on the way out its dx boxes and its row of dA) are all 2-D tiled copies that differ only in
+// descriptor, shared-memory address and coordinates.  Lane i of the warp keeps copy i's parameters in its own
+// registers and all the lanes concerned execute ONE copy instruction together, instead of one lane issuing
+// them one after the other: the per-chunk producer code shrinks to a handful of warp instructions.
+struct LaneCopy {
+  uint64_t map;    // generic address of the descriptor (a __grid_constant__ kernel parameter)
+  uint32_t cur;    // shared-memory address in the ring's current stage
+  uint32_t first;  // ... in stage 0
+  uint32_t end;    // first + stages * stride
+  uint32_t stride; // bytes from one stage to the next
+  int col_off;     // added to the chunk's first token
+  int row_mul;     // row coordinate = sequence index * row_mul (16 channel rows, or 1 row of coefficients)
+  __device__ __forceinline__ void set(const void* m, uint32_t first_, uint32_t stride_, int stages, int col, int rows) {
+    map = reinterpret_cast<uint64_t>(m);
+    cur = first = first_;
+    stride = stride_;
+    end = first_ + stages * stride_;
+    col_off = col;
+    row_mul = rows;
+  }
+  __device__ __forceinline__ void advance() {
+    cur += stride;
+    if (cur == end) cur = first;
+  }
+  __device__ __forceinline__ uint32_t at(int stage) const { return first + stage * stride; }
+};
+
 // Position of a chunk; walks forward one chunk at a time (no division after the first).
 struct ChunkCursor {
   int bh;    // sequence index
@@ -503,11 +531,10 @@ __device__ __forceinline__ void report_error(unsigned int code, int warp, int ch
 template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
-                   const KernelParams p) {
+                   const __grid_constant__ CUtensorMap tm_c, const KernelParams p) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
   constexpr int TL = LAYOUT::kTL;
   constexpr int NT = LAYOUT::kTiles;
-  constexpr int kEsz = CoefTraits<COEF>::kBytes;
   // Loads run AHEAD chunks in front of the one being computed.  A bf16 output leaves through the
   // stage buffer itself, so a stage is reloaded only two chunks after its store was issued.
   constexpr int AHEAD = OUT_F32 ? STAGES - 1 : STAGES - 2;
@@ -535,6 +562,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     mbar_init_fence();
     fence_proxy_async_smem();
     prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_c);
     if (!OUT_F32) prefetch_tensormap(&tm_y);
     // test hook for the give-up path: bytes that no copy will ever deliver keep this warp's first wait pending
     if (p.test_missing_tx != 0 && blockIdx.x == 0 && warp == 0) mbar_expect_tx(ws.bar(0), p.test_missing_tx);
@@ -546,20 +574,20 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const float carry_scale = p.use_carry ? 1.0f : 0.0f;
   RunCursor prod = cons;
   int s_prod = 0;
+  // Loads of a chunk: lanes 0 .. NBOX-1 fetch its x boxes, lane NBOX its row of coefficients (see LaneCopy).
+  // A ragged last chunk is fetched whole as well: what lies beyond the sequence arrives as zeros and still
+  // counts towards the barrier's byte count, so the count is a constant.
+  constexpr uint32_t kChunkBytes = LAYOUT::kXBytes + LAYOUT::kRawBytes;
+  LaneCopy ld;
+  if (lane < NBOX) ld.set(&tm_x, ws.x(0) + lane * 2048, LAYOUT::kXBytes, STAGES, 64 * lane, 16);
+  else ld.set(&tm_c, ws.raw_addr(0), LAYOUT::kRawBytes, STAGES, 0, 1);
   auto issue = [&]() {  // starts the loads of the producer cursor's chunk into stage s_prod, then advances
-    if (lane == 0) {
-      const int nt = chunk_tiles<TL, RAGGED>(prod.cs, L);
-      const int c0 = prod.cs * TL;
-      const int nbox = (nt + 3) >> 2;
-      const uint32_t cbytes = nt * 16 * kEsz;
-      const uint32_t bar = ws.bar(s_prod);
-      mbar_arrive_expect_tx(bar, nbox * 2048 + cbytes);
-#pragma unroll
-      for (int b = 0; b < NBOX; ++b)
-        if (b < nbox) tma_load_2d(ws.x(s_prod) + b * 2048, &tm_x, c0 + 64 * b, prod.bh * 16, bar);
-      bulk_load(ws.raw_addr(s_prod),
-                reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(prod.bh) * L + c0) * kEsz, cbytes, bar);
+    const uint32_t bar = ws.bar(s_prod);
+    if (lane <= NBOX) {
+      if (lane == 0) mbar_arrive_expect_tx(bar, kChunkBytes);
+      tma_load_2d(ld.cur, ld.map, prod.cs * TL + ld.col_off, prod.bh * ld.row_mul, bar);
     }
+    ld.advance();
     prod.next(ncs);
     s_prod = (s_prod + 1 == STAGES) ? 0 : s_prod + 1;
   };
@@ -573,7 +601,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   for (; j < n; ++j) {
     if (j + AHEAD < n) {
-      if (!OUT_F32 && lane == 0) bulk_wait_group_read<1>();  // the store that last used that stage has drained
+      if (!OUT_F32 && lane < NBOX) bulk_wait_group_read<1>();  // this lane's store that last used that stage has drained
       issue();
     }
     // the decision to give up is taken by the whole warp: the code below is full of warp-wide instructions
@@ -627,11 +655,15 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         }
         const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
         const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);
-        float y0[4], y1[4];
-        y0[0] = fmaf(Pa.x, cg, v0[0]);  y0[1] = fmaf(Pa.y, cg, v0[1]);
-        y0[2] = fmaf(Pa.x, cg8, v0[2]); y0[3] = fmaf(Pa.y, cg8, v0[3]);
-        y1[0] = fmaf(Pb.x, cg, v1[0]);  y1[1] = fmaf(Pb.y, cg, v1[1]);
-        y1[2] = fmaf(Pb.x, cg8, v1[2]); y1[3] = fmaf(Pb.y, cg8, v1[3]);
+        // y = v + P (x) carry, a token pair per packed fp32x2 instruction (the accumulators hold tokens
+        // 2t, 2t+1 of a channel side by side)
+        const float2 cg2 = make_float2(cg, cg), cg82 = make_float2(cg8, cg8);
+        const float2 ya = __ffma2_rn(Pa, cg2, make_float2(v0[0], v0[1]));
+        const float2 yb = __ffma2_rn(Pa, cg82, make_float2(v0[2], v0[3]));
+        const float2 yc = __ffma2_rn(Pb, cg2, make_float2(v1[0], v1[1]));
+        const float2 yd = __ffma2_rn(Pb, cg82, make_float2(v1[2], v1[3]));
+        const float y0[4] = {ya.x, ya.y, yb.x, yb.y};
+        const float y1[4] = {yc.x, yc.y, yd.x, yd.y};
         if constexpr (CKPT) {
           // slot j of the checkpoint = block-local last token of block j, except the last block
           if (p.use_carry && tl.t == 3 && (cons.cs * NT + i) < (L >> 4) - 1) {
@@ -649,7 +681,9 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           *reinterpret_cast<float2*>(yo + 16 * i + 8) = make_float2(y1[0], y1[1]);
           *reinterpret_cast<float2*>(yo + 16 * i + 8 + r8) = make_float2(y1[2], y1[3]);
         } else {
-          __syncwarp();  // all lanes have consumed this block's x before it is overwritten
+          // y replaces the consumed x block.  No warp barrier is needed in between: the block was read by ONE
+          // warp-wide ldmatrix, the products that y depends on wait for that whole instruction, and the
+          // shared-memory instructions of a warp execute in program order.
           const uint32_t o0 = stb + box * 2048 + tl.st_off[ib];
           const uint32_t o1 = o0 ^ 16u;
           st_shared_u32(o0, pack_bf16x2(y0[0], y0[1]));
@@ -662,11 +696,8 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if constexpr (!OUT_F32) {
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        const int nbox = (nt + 3) >> 2;
-#pragma unroll
-        for (int b = 0; b < NBOX; ++b)
-          if (b < nbox) tma_store_2d(&tm_y, c0 + 64 * b, cons.bh * 16, xs + b * 2048);
+      if (lane < NBOX) {  // lane b sends box b (the same lane reloads that box's buffer later)
+        if (!RAGGED || c0 + 64 * lane < L) tma_store_2d(&tm_y, c0 + 64 * lane, cons.bh * 16, xs + lane * 2048);
         bulk_commit_group();
       }
     }
@@ -688,7 +719,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       }
     }
   }
-  if (!OUT_F32 && lane == 0) bulk_wait_group<0>();
+  if (!OUT_F32 && lane < NBOX) bulk_wait_group<0>();
 }
 
 // =====================================================================================
@@ -704,11 +735,11 @@ struct TileAcc {
 template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
-                    const __grid_constant__ CUtensorMap tm_dx, const KernelParams p) {
+                    const __grid_constant__ CUtensorMap tm_dx, const __grid_constant__ CUtensorMap tm_c,
+                    const __grid_constant__ CUtensorMap tm_da, const KernelParams p) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, true, DY_F32>;
   constexpr int TL = LAYOUT::kTL;
   constexpr int NT = LAYOUT::kTiles;
-  constexpr int kEsz = CoefTraits<COEF>::kBytes;
   static_assert(STAGES >= 3, "the backward ring needs three stages");
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -735,6 +766,8 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_dy);
     prefetch_tensormap(&tm_dx);
+    prefetch_tensormap(&tm_c);
+    prefetch_tensormap(&tm_da);
     if (p.test_missing_tx != 0 && blockIdx.x == 0 && warp == 0) mbar_expect_tx(ws.bar(0), p.test_missing_tx);  // see forward
   }
   __syncwarp();
@@ -743,35 +776,38 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   const int L = p.L, ncs = p.ncs;
   const float carry_scale = p.use_carry ? 1.0f : 0.0f;
   ChunkCursor prod(work.bh, work.cs, work.step), cons(work.bh, work.cs, work.step);
-  int s_prod = 0, d_prod = 0, issued = 0;
+  int s_prod = 0, issued = 0;
+  // Loads of a chunk (see LaneCopy): lanes 0 .. NBOX-1 its x boxes, the next NDY lanes its dy boxes (a float dy
+  // takes two 32-token boxes per 64 tokens), the lane after them its row of coefficients.  The dy ring is one
+  // stage shorter than the x ring; every lane steps through its own ring.  Ragged chunks are fetched whole.
+  constexpr int NDY = DY_F32 ? 2 * NBOX : NBOX;
+  constexpr int kLoadLanes = NBOX + NDY + 1;
+  constexpr uint32_t kChunkBytes = LAYOUT::kXBytes + LAYOUT::kDyBytes + LAYOUT::kRawBytes;
+  LaneCopy ld;
+  if (lane < NBOX) ld.set(&tm_x, ws.x(0) + lane * 2048, LAYOUT::kXBytes, STAGES, 64 * lane, 16);
+  else if (lane < NBOX + NDY) ld.set(&tm_dy, ws.dy(0) + (lane - NBOX) * 2048, LAYOUT::kDyBytes, STAGES - 1,
+                                     (DY_F32 ? 32 : 64) * (lane - NBOX), 16);
+  else ld.set(&tm_c, ws.raw_addr(0), LAYOUT::kRawBytes, STAGES, 0, 1);
+  // Stores of a chunk: lanes 0 .. NBOX-1 its dx boxes (out of the x buffers), lane NBOX its row of dA.
+  LaneCopy st;
+  if (lane < NBOX) st.set(&tm_dx, ws.x(0) + lane * 2048, LAYOUT::kXBytes, STAGES, 64 * lane, 16);
+  else st.set(&tm_da, ws.da_addr(0), LAYOUT::kDaBytes, STAGES, 0, 1);
   auto issue = [&]() {
-    if (lane == 0) {
-      const int nt = chunk_tiles<TL, RAGGED>(prod.cs, L);
-      const int c0 = prod.cs * TL;
-      const int nbox = (nt + 3) >> 2;
-      const int nbox_dy = DY_F32 ? (nt + 1) >> 1 : nbox;
-      const uint32_t cbytes = nt * 16 * kEsz;
-      const uint32_t bar = ws.bar(s_prod);
-      mbar_arrive_expect_tx(bar, (nbox + nbox_dy) * 2048 + cbytes);
-#pragma unroll
-      for (int b = 0; b < NBOX; ++b)
-        if (b < nbox) tma_load_2d(ws.x(s_prod) + b * 2048, &tm_x, c0 + 64 * b, prod.bh * 16, bar);
-#pragma unroll
-      for (int b = 0; b < (DY_F32 ? 2 * NBOX : NBOX); ++b)
-        if (b < nbox_dy) tma_load_2d(ws.dy(d_prod) + b * 2048, &tm_dy, c0 + (DY_F32 ? 32 : 64) * b, prod.bh * 16, bar);
-      bulk_load(ws.raw_addr(s_prod),
-                reinterpret_cast<const char*>(p.coeff) + (static_cast<long long>(prod.bh) * L + c0) * kEsz, cbytes, bar);
+    const uint32_t bar = ws.bar(s_prod);
+    if (lane < kLoadLanes) {
+      if (lane == 0) mbar_arrive_expect_tx(bar, kChunkBytes);
+      tma_load_2d(ld.cur, ld.map, prod.cs * TL + ld.col_off, prod.bh * ld.row_mul, bar);
     }
+    ld.advance();
     prod.next(ncs);
     s_prod = (s_prod + 1 == STAGES) ? 0 : s_prod + 1;
-    d_prod = (d_prod + 1 == STAGES - 1) ? 0 : d_prod + 1;
     ++issued;
   };
 
   // Chunk j's outputs leave one block into chunk j+1 (its last block needs the gradient that
-  // arrives from the right).  The x buffer of chunk j is reloaded one chunk later still, when that
+  // arrives from the right).  The x buffer of chunk j is reloaded at the end of chunk j+1, when that
   // store has certainly drained; the dy buffer of chunk j is free once chunk j's products are done.
-  // Loads therefore run STAGES-2 chunks ahead, and STAGES-1 dy buffers are enough.
+  // Loads therefore run a whole chunk ahead of the one in work, and STAGES-1 dy buffers are enough.
   while (issued < STAGES - 1 && issued < n) issue();
 
   // ---- front half of a block: Lmat fragments and the four tensor-core products
@@ -909,16 +945,19 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   auto flush = [&]() {  // the pending block's chunk is complete: send dx and dA on their way
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) {
-      const int nbox = (p_nt + 3) >> 2;
-#pragma unroll
-      for (int b = 0; b < NBOX; ++b)
-        if (b < nbox) tma_store_2d(&tm_dx, p_c0 + 64 * b, p_bh * 16, ws.x(p_stage) + b * 2048);
-      bulk_store(p.dA + static_cast<long long>(p_bh) * L + p_c0, ws.da_addr(p_stage), p_nt * 64);
+    if (lane <= NBOX) {
+      // a ragged chunk is stored whole too: the copy clips what lies beyond the sequence
+      if (!RAGGED || p_c0 + st.col_off < L) tma_store_2d(st.map, p_c0 + st.col_off, p_bh * st.row_mul, st.at(p_stage));
       bulk_commit_group();
-      if (issued < n) bulk_wait_group_read<1>();  // the store flushed one chunk earlier has drained
     }
-    if (issued < n) issue();
+  };
+  // The loads of chunk j+1 start as soon as chunk j-1's last products are done: its dy buffer is dead then, and the
+  // x buffer it goes into last held chunk j-2, whose store left three blocks ago and has long been read out.
+  auto issue_next = [&]() {
+    if (issued < n) {
+      if (lane <= NBOX) bulk_wait_group_read<0>();
+      issue();
+    }
   };
 
   int j = 0, s = 0, d = 0, tset = 0;
@@ -979,6 +1018,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     p_bh = cons.bh;
     p_c0 = c0;
     p_nt = nt;
+    issue_next();
     cons.next(ncs);
     tset ^= 1;
     if (++d == STAGES - 1) d = 0;
@@ -1007,7 +1047,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       }
     }
   }
-  if (lane == 0) bulk_wait_group<0>();
+  if (lane <= NBOX) bulk_wait_group<0>();
 }
 
 }  // namespace btp

@@ -36,16 +36,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One probe of the barrier.  The thread may be suspended by the hardware for up to kTryWaitHintNs while the phase
+// is incomplete (it is woken as soon as the phase completes), so that a warp whose data is still on its way
+// does not fill the issue slots of its neighbours with polling.
+#ifndef BTP_TRY_WAIT_HINT_NS
+#define BTP_TRY_WAIT_HINT_NS 1000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       "  .reg .pred p;\n"
-      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "  selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(BTP_TRY_WAIT_HINT_NS))
       : "memory");
   return ok != 0;
 }
@@ -84,18 +90,24 @@ __device__ __forceinline__ void bulk_wait_group() {
 
 // ---------------------------------------------------------------- TMA (no multicast anywhere)
 // 2-D tiled load global -> shared, completion on an mbarrier.  c0 = innermost coordinate.
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+// `map` is the generic address of a descriptor (kernel parameter, constant or global memory).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, uint64_t map, int c0, int c1, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  tma_load_2d(dst, reinterpret_cast<uint64_t>(map), c0, c1, bar);
+}
 // 2-D tiled store shared -> global (bulk async-group).
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(c0), "r"(c1), "r"(src)
+__device__ __forceinline__ void tma_store_2d(uint64_t map, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0),
+               "r"(c1), "r"(src)
                : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+  tma_store_2d(reinterpret_cast<uint64_t>(map), c0, c1, src);
 }
 // Untiled bulk load global -> shared (16-byte aligned addresses, size % 16 == 0).
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

@@ -58,55 +58,57 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // Encoded descriptors, remembered per calling thread: a descriptor depends only on (base address, element type,
-// rows, L), a training loop presents the same few tensors again and again, and encoding one costs about a
-// microsecond of host time - as much as the rest of a call.  Thread-local, so no lock; 16 entries, replaced
-// round-robin.  (A descriptor holds no device state: reusing one for a buffer that was freed and allocated
-// again at the same address with the same shape is correct.)
+// rows, L, box), a training loop presents the same few tensors again and again, and encoding one costs about a
+// microsecond of host time - as much as the rest of a call.  Thread-local, so no lock; 128 direct-mapped slots.
+// (A descriptor holds no device state: reusing one for a buffer that was freed and allocated again at the same
+// address with the same shape is correct.)
+struct MapShape {
+  int esz;       // element size: 2 (bf16) or 4 (float)
+  int box_cols;  // box width in elements
+  int box_rows;
+  bool swizzle;  // 128-byte swizzle (the 16-row activation boxes) or none (single coefficient / dA rows)
+};
+constexpr MapShape kActBf16{2, 64, 16, true};   // x, y, dy, dx: [16 channels][64 tokens]
+constexpr MapShape kActF32{4, 32, 16, true};    // float dy: [16 channels][32 tokens]
+inline MapShape row_shape(int esz, int cols) { return MapShape{esz, cols, 1, false}; }  // one row of coeff / dA
+
 struct MapCacheEntry {
   const void* base = nullptr;
   long long rows = 0;
   int L = 0;
-  int kind = -1;  // 0: bf16 rows of x/y/dy/dx, 1: float rows of dy
+  unsigned shape = 0;
   CUtensorMap map;
 };
-struct MapCache {
-  MapCacheEntry e[16];
-  unsigned next = 0;
-};
-thread_local MapCache tls_maps;
+thread_local MapCacheEntry tls_maps[128];
 
-int encode_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L);
-
-// [rows = BH*16][cols = L] tensor, box = 16 rows x one 128-byte swizzle span.
-int make_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L) {
-  MapCache& c = tls_maps;
-  const int kind = f32 ? 1 : 0;
-  for (const MapCacheEntry& e : c.e) {
-    if (e.base == base && e.rows == rows && e.L == L && e.kind == kind) {
-      *map = e.map;
-      return BTP_OK;
-    }
-  }
-  const int rc = encode_map(map, base, f32, rows, L);
-  if (rc) return rc;
-  MapCacheEntry& slot = c.e[c.next++ & 15u];
-  slot.base = base; slot.rows = rows; slot.L = L; slot.kind = kind; slot.map = *map;
+int encode_map(CUtensorMap* map, const void* base, MapShape sh, long long rows, int L) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(L) * sh.esz};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(sh.box_cols), static_cast<cuuint32_t>(sh.box_rows)};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = enc(map, sh.esz == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         sh.swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
   return BTP_OK;
 }
 
-int encode_map(CUtensorMap* map, const void* base, bool f32, long long rows, int L) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint32_t esz = f32 ? 4 : 2;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(L) * esz};
-  const cuuint32_t box[2] = {128u / esz, 16u};
-  const cuuint32_t estr[2] = {1u, 1u};
-  const CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+// Descriptor of a [rows][L] tensor read or written in boxes of shape `sh`.
+int make_map(CUtensorMap* map, const void* base, MapShape sh, long long rows, int L) {
+  const unsigned shape = static_cast<unsigned>(sh.esz) | static_cast<unsigned>(sh.box_cols) << 4 |
+                         static_cast<unsigned>(sh.box_rows) << 16 | (sh.swizzle ? 1u << 24 : 0u);
+  const uintptr_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull + shape * 0x85EBCA6Bu;
+  MapCacheEntry& e = tls_maps[(h >> 40) & 127u];
+  if (e.base == base && e.rows == rows && e.L == L && e.shape == shape) {
+    *map = e.map;
+    return BTP_OK;
+  }
+  const int rc = encode_map(map, base, sh, rows, L);
+  if (rc) return rc;
+  e.base = base; e.rows = rows; e.L = L; e.shape = shape; e.map = *map;
   return BTP_OK;
 }
 
@@ -199,7 +201,8 @@ struct Launcher {
 // kernel of the stream still runs; its CTAs start when that kernel's CTAs have all exited and wait in pdl_wait()
 // until its memory is visible.  That hides the launch latency (-2 % on the forward+backward step at
 // B=1024, H=32, L=128).  The kernels do NOT release their successor early (griddepcontrol.launch_dependents at
-// kernel start was measured 9 % slower: the successor's CTAs then occupy SMs while the stragglers finish).
+// kernel start was measured 9 % slower: the successor's CTAs then occupy SMs while the stragglers finish;
+// at the end of each warp's work it was measured within 0.6 % of not doing it).
 // BTP_SM100_PDL=0 launches the plain way.
 bool use_pdl() {
   static const bool v = [] {
@@ -285,13 +288,14 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
   int ctas;
   if ((rc = L.prepare(dev, &ctas))) return rc;
   if ((rc = set_chunks("btp_sm100_forward", &d, LAYOUT::kTL))) return rc;
-  CUtensorMap tm_x, tm_y;
-  if ((rc = make_map(&tm_x, x, false, d.BH * 16, d.L))) return rc;
+  CUtensorMap tm_x, tm_y, tm_c;
+  if ((rc = make_map(&tm_x, x, kActBf16, d.BH * 16, d.L))) return rc;
   if (OUT_F32) {
     tm_y = tm_x;  // unused by the kernel
-  } else if ((rc = make_map(&tm_y, y, false, d.BH * 16, d.L))) {
+  } else if ((rc = make_map(&tm_y, y, kActBf16, d.BH * 16, d.L))) {
     return rc;
   }
+  if ((rc = make_map(&tm_c, coeff, row_shape(CoefTraits<COEF>::kBytes, LAYOUT::kTL), d.BH, d.L))) return rc;
   const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
   KernelParams p{};
   p.coeff = coeff; p.x = x; p.out_f32 = y; p.ckpt = ckpt;
@@ -300,7 +304,7 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
   p.interleave = p.run_len == d.ncs;
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
-  BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_y, p));
+  BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_y, tm_c, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
 }
@@ -343,10 +347,12 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
   int ctas;
   if ((rc = L.prepare(dev, &ctas))) return rc;
   if ((rc = set_chunks("btp_sm100_backward", &d, LAYOUT::kTL))) return rc;
-  CUtensorMap tm_x, tm_dy, tm_dx;
-  if ((rc = make_map(&tm_x, x, false, d.BH * 16, d.L))) return rc;
-  if ((rc = make_map(&tm_dy, dy, DY_F32, d.BH * 16, d.L))) return rc;
-  if ((rc = make_map(&tm_dx, dx, false, d.BH * 16, d.L))) return rc;
+  CUtensorMap tm_x, tm_dy, tm_dx, tm_c, tm_da;
+  if ((rc = make_map(&tm_x, x, kActBf16, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_dy, dy, DY_F32 ? kActF32 : kActBf16, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_dx, dx, kActBf16, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_c, coeff, row_shape(CoefTraits<COEF>::kBytes, LAYOUT::kTL), d.BH, d.L))) return rc;
+  if ((rc = make_map(&tm_da, dA, row_shape(4, LAYOUT::kTL), d.BH, d.L))) return rc;
   const int grid = L.grid_for(info.sms, ctas, d.total_chunks);
   KernelParams p{};
   p.coeff = coeff; p.x = x; p.dy = dy; p.dA = dA;
@@ -354,7 +360,7 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
   p.interleave = use_interleave(d, static_cast<long long>(grid) * WARPS);
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
-  BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_dy, tm_dx, p));
+  BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_dy, tm_dx, tm_c, tm_da, p));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
 }
