@@ -123,10 +123,14 @@ class ClockSampler:
         }
 
 
+COEFF_KIND = "bf16"
+
+
 def workload_string() -> str:
     """One string for both arms, so that the two JSON lines name the same configuration."""
-    return (f"btp fwd+bwd B={B} H={H} L={L} head_dim={D} block=16 per GPU (configs[2]); "
-            "x~N(0,1/16) bf16, coeff=exp(-softplus(N(0,1))) bf16, dy~N(0,1) bf16")
+    which = " (configs[2])" if (B, H, L, COEFF_KIND) == (1024, 32, 128, "bf16") else ""
+    coeff = "coeff=exp(-softplus(N(0,1))) bf16" if COEFF_KIND == "bf16" else "coeff=log a~U(-1e-3,0) float32"
+    return f"btp fwd+bwd B={B} H={H} L={L} head_dim={D} block=16 per GPU{which}; x~N(0,1/16) bf16, {coeff}, dy~N(0,1) bf16"
 
 
 def load_cpu_reference():
@@ -207,7 +211,7 @@ def run_reference_arm(args, rank):
 
 
 def main():
-    global B
+    global B, H, L, COEFF_KIND
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -217,12 +221,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations and the strong-scaling line")
     ap.add_argument("--batch", type=int, default=B, help="batch entries per GPU (default: the benchmark workload)")
+    ap.add_argument("--heads", type=int, default=H, help="heads (default: the benchmark workload)")
+    ap.add_argument("--length", type=int, default=L, help="tokens per sequence (default: the benchmark workload)")
+    ap.add_argument("--coeff", default="bf16", choices=["bf16", "f32log"],
+                    help="bf16: a = exp(-softplus(N(0,1))) in bf16; f32log: log a ~ U(-1e-3, 0) in float32")
     ap.add_argument("--sets", type=int, default=3, help="rotating input/output sets")
     ap.add_argument("--kernel-launches", type=int, default=200, help="launches per per-kernel timing loop")
     ap.add_argument("--kernel-repeats", type=int, default=5, help="repeats of each per-kernel timing loop")
     args = ap.parse_args()
 
-    B = args.batch
+    B, H, L = args.batch, args.heads, args.length
+    COEFF_KIND = args.coeff
+    log_coeff = args.coeff == "f32log"
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -249,7 +259,7 @@ def main():
 
     from spear_b200 import _btp, _lib
     from spear_b200.ops.btp import btp
-    from spear_b200.sharding import batch_shard, max_over_ranks, sum_over_ranks
+    from spear_b200.sharding import batch_shard, bind_to_gpu_numa_node, max_over_ranks, sum_over_ranks
 
     _lib.load()
     dev = torch.device("cuda", local_rank)
@@ -296,12 +306,12 @@ def main():
 
     # ---- inputs resident in HBM; NSETS rotating sets (each step touches 705 MB, the L2 holds 126 MB)
     NSETS = max(1, args.sets)
-    sets = make_sets(B, H, L, NSETS)
+    sets = make_sets(B, H, L, NSETS, args.coeff)
 
     def step(i):
         a, x, dy, y, dx, dA = sets[i % NSETS]
-        _btp.forward(a, x, y, None, 2, 32)
-        _btp.backward(a, x, dy, None, dx, dA, 2, 32)
+        _btp.forward(a, x, y, None, 2, 32, log_coeff=log_coeff)
+        _btp.backward(a, x, dy, None, dx, dA, 2, 32, log_coeff=log_coeff)
 
     for i in range(args.warmup):
         step(i)
@@ -327,11 +337,11 @@ def main():
 
     def launch_fwd(i):
         a, x, dy, y, dx, dA = sets[i % NSETS]
-        _btp.forward(a, x, y, None, 2, 32)
+        _btp.forward(a, x, y, None, 2, 32, log_coeff=log_coeff)
 
     def launch_bwd(i):
         a, x, dy, y, dx, dA = sets[i % NSETS]
-        _btp.backward(a, x, dy, None, dx, dA, 2, 32)
+        _btp.backward(a, x, dy, None, dx, dA, 2, 32, log_coeff=log_coeff)
 
     fwd_runs = loop_us(launch_fwd, nk, reps)
     bwd_runs = loop_us(launch_bwd, nk, reps)
@@ -350,7 +360,9 @@ def main():
     bwd_single_us = statistics.mean(e[1].elapsed_time(e[2]) for e in evs) * 1e3
     _lib.device_status()
 
-    # ---- timed region 2: end to end with pinned host buffers
+    # ---- timed region 2: end to end with pinned host buffers.  With several ranks on the box each rank first moves
+    #      to the cores next to its GPU, so that the pinned pages it is about to touch land on that socket's memory.
+    numa_cores = bind_to_gpu_numa_node(local_rank) if world > 1 else []
     ha = sets[0][0].cpu().pin_memory()
     hx = sets[0][1].cpu().pin_memory()
     hdy = sets[0][2].cpu().pin_memory()
@@ -407,6 +419,8 @@ def main():
         return f0.elapsed_time(f1)
 
     e2e_ms = e2e_autograd_ms = floor_ms = float("nan")
+    if log_coeff:
+        args.e2e_steps = 0  # the host-buffer entry takes linear coefficients
     if args.e2e_steps > 0:
         e2e_autograd_ms = time_e2e(e2e_step)
         e2e_ms = time_e2e(e2e_step_pipelined)
@@ -477,10 +491,11 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_peak()
         ht = B * H * L
-        bwd_gbs = BWD_BYTES_PER_HT * ht / (bwd_us * 1e-6) / 1e9
-        fwd_gbs = FWD_BYTES_PER_HT * ht / (fwd_us * 1e-6) / 1e9
+        fwd_b, bwd_b = FWD_BYTES_PER_HT + (2 if log_coeff else 0), BWD_BYTES_PER_HT + (2 if log_coeff else 0)
+        bwd_gbs = bwd_b * ht / (bwd_us * 1e-6) / 1e9
+        fwd_gbs = fwd_b * ht / (fwd_us * 1e-6) / 1e9
         step_us = total_ms * 1e3 / args.steps
-        step_gbs = (FWD_BYTES_PER_HT + BWD_BYTES_PER_HT) * ht / (step_us * 1e-6) / 1e9
+        step_gbs = (fwd_b + bwd_b) * ht / (step_us * 1e-6) / 1e9
         value = world * B * L * args.steps / (total_ms * 1e-3)
         for v in extra.values():
             if isinstance(v, dict) and "fwd_gbs" in v:
@@ -493,7 +508,7 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": {
                 "workload": workload_string(),
-                "l2": f"each step touches {168 * B * H * L / 1e6:.0f} MB (L2 holds 126 MB) and {NSETS} input/output sets rotate",
+                "l2": f"each step touches {(fwd_b + bwd_b) * B * H * L / 1e6:.0f} MB (L2 holds 126 MB) and {NSETS} input/output sets rotate",
                 "parallelism": f"batch sharded over {world} GPU(s), no data-path collective",
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "per_gpu": e2e_value / world,
@@ -501,6 +516,8 @@ def main():
                     "pcie_floor_ms": floor_ms / max(1, args.e2e_steps),
                     "pcie_floor": f"the same bytes as plain pinned copies, both directions at once, on all {world} rank(s) at the same time",
                     "frac_of_pcie_floor": floor_ms / e2e_ms,
+                    "host_placement": (f"rank 0 bound to {len(numa_cores)} cores next to its GPU before pinning its buffers"
+                                       if numa_cores else "default placement"),
                     "api": "spear_b200.ops.btp.btp_fwd_bwd_host (pinned host tensors in and out, batch slices on 3 streams)",
                     "via_btp_autograd": {"value": world * B * L * args.e2e_steps / (e2e_autograd_ms * 1e-3), "unit": UNIT,
                                          "api": "tensor.to(device) + btp() + backward() + copy_ to host, one stream"}},
@@ -514,12 +531,12 @@ def main():
                          "us_per_launch_between_event_records": bwd_single_us,
                          "method": f"{nk} back-to-back launches of the kernel between two CUDA events on the launching stream, "
                                    f"median of {reps} repeats",
-                         "algorithmic_bytes_per_launch": BWD_BYTES_PER_HT * ht},
+                         "algorithmic_bytes_per_launch": bwd_b * ht},
             "roofline_forward": {"bound": "hbm", "kernel": "btp_forward_kernel", "achieved": fwd_gbs, "peak": peak,
                                  "unit": "GB/s", "frac": fwd_gbs / peak, "us_per_launch": fwd_us,
                                  "us_per_launch_best": min(fwd_runs), "us_per_launch_runs": fwd_runs,
                                  "us_per_launch_between_event_records": fwd_single_us,
-                                 "algorithmic_bytes_per_launch": FWD_BYTES_PER_HT * ht},
+                                 "algorithmic_bytes_per_launch": fwd_b * ht},
             "step_hbm": {"achieved_gbs": step_gbs, "frac_of_measured": step_gbs / peak,
                          "frac_of_nominal_8TBs": step_gbs / NOMINAL_HBM_GBS, "us_per_step": step_us},
         }

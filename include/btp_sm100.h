@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define BTP_SM100_ABI_VERSION 2
+#define BTP_SM100_ABI_VERSION 3
 
 /* status codes */
 #define BTP_OK 0
@@ -128,11 +128,14 @@ int btp_sm100_noalloc_read_record(float* dst, long long n_floats, void* stream);
  *   c, v      [B, L, H*16]   bf16, pitches ld_c, ld_v } the four inputs may be column slices of one wide
  *   out       [B, L, H*16]   bf16, pitch ld_out      /  projection output
  *   H % 4 == 0, L % 16 == 0, k as in btp_sm100_forward.
+ *   kv_heads  number of key/value heads, a divisor of H.  With kv_heads < H, b_logits and c are
+ *             [B, L, kv_heads*16] and head h uses the columns of key/value head h / (H / kv_heads), as KVRepeat
+ *             does (spear/nn/phalanx/swr.py:96-103, 209-214) - read in place, nothing is repeated in memory.
  * out = btp(sigmoid(a_logits), sigmoid(b_logits) * v) * c + v, with the decay rounded to bf16 as the layer does.
  */
 int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out,
-                            int B, int L, int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
-                            long long ld_out, int k, void* stream);
+                            int B, int L, int H, int kv_heads, long long ld_a, long long ld_b, long long ld_c,
+                            long long ld_v, long long ld_out, int k, void* stream);
 
 /*
  * Backward of btp_sm100_gated_forward, token-major throughout.  Replaces autograd through
@@ -142,9 +145,12 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
  *   da_logits                 [B, L, H]    bf16  (pitch a multiple of 4 elements, base 8-byte aligned)
  *   db_logits, dc, dv         [B, L, H*16] bf16
  * Pitches (elements) follow the pointers in the same order; constraints as for the forward.
+ * With kv_heads < H, b_logits and c are [B, L, kv_heads*16] (read in place, as in the forward) while db_logits
+ * and dc are still written PER HEAD, [B, L, H*16]: the gradient of a shared key/value head is the sum of these
+ * over the heads of its group, which is left to the caller (one reduction; autograd does the same for KVRepeat).
  */
 int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
-                             void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H,
+                             void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, int kv_heads,
                              long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_do,
                              long long ld_da, long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream);
 
@@ -199,7 +205,7 @@ int btp_sm100_device_status(void* stream, unsigned int* detail);
 /*
  * How long a wait inside a kernel may last before the kernel gives up, records the error word that
  * btp_sm100_device_status reports, lets its copies in flight land and returns (default 2 s; 0 restores the
- * default).  Applies to the forward and backward launches that follow, process-wide.  Returns the previous
+ * default).  Applies to every launch that follows, process-wide.  Returns the previous
  * value.  No counterpart in the reference, whose kernels wait on cluster barriers without a bound
  * (csrc/btp/btp-forward.cu:340-347).
  */

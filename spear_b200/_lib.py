@@ -19,7 +19,7 @@ DTYPE_BF16 = 0
 DTYPE_F32 = 1
 DTYPE_F32_LOG = 2
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # every symbol include/btp_sm100.h declares: name -> (restype, argtypes)
 _vp, _i, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
@@ -27,8 +27,8 @@ SYMBOLS = {
     "btp_sm100_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_forward_noalloc": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
-    "btp_sm100_gated_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _vp]),
-    "btp_sm100_gated_backward": (_i, [_vp] * 9 + [_i, _i, _i] + [_ll] * 9 + [_i, _vp]),
+    "btp_sm100_gated_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _vp]),
+    "btp_sm100_gated_backward": (_i, [_vp] * 9 + [_i, _i, _i, _i] + [_ll] * 9 + [_i, _vp]),
     "btp_sm100_decode_step": (_i, [_vp] * 11 + [_ll, _i, _i, _i, _i, _i, _vp]),
     "btp_sm100_prefill_state": (_i, [_vp] * 5 + [_ll, _i, _i, _i, _i, _vp]),
     "btp_sm100_noalloc_read_record": (_i, [_vp, _ll, _vp]),

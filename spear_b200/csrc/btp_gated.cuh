@@ -16,6 +16,11 @@
 // y*C+V in the accumulator layout and puts the result back over V with stmatrix.trans; one thread then
 // stores the box.  The CTA walks along sequences, so the carry stays in registers; a CTA whose range starts
 // inside a sequence recomputes the carry of the block to its left from global memory.
+//
+// Shared key/value heads (SHARED == true; KVRepeat, swr.py:96-103: head h reads key/value head h / group).
+// B_logits and C are then [B, L, kv_heads*16] and are read IN PLACE: each warp fetches the 16 columns of its
+// key/value head as its own dense [tokens][16 channels] tile (32-byte rows, no swizzle), so the heads of a group
+// fetch the same global columns - once from HBM, the repeats from L2 - and nothing is repeated in memory.
 #pragma once
 
 #include "btp_kernels.cuh"
@@ -34,6 +39,8 @@ struct GatedParams {
   int total_units;                // B * hgs * ncs
   int use_carry;                  // k == 2
   int interleave;                 // deal whole sequences round-robin to the CTAs
+  int group;                      // heads per key/value head: head h reads columns (h / group) * 16 of B_logits and C
+  unsigned long long wait_limit_ns;  // bounded waits give up after this long (btp_sm100_set_wait_limit)
 };
 
 // TL = tokens per chunk (32 or 64): one box is [TL tokens][64 channels] bf16.
@@ -81,7 +88,7 @@ __device__ __forceinline__ void gated_halo_left(const GatedParams& p, long long 
   for (int j = 0; j < 4; ++j) {
     const int tok = 2 * t + (j & 1) + ((j >> 1) << 3);
     const float w = lmat_weight<true>(ex2(T15 - __shfl_sync(0xffffffffu, T, tok)));
-    const long long rb = (row0 + tok) * p.ld_b + h * 16;
+    const long long rb = (row0 + tok) * p.ld_b + (h / p.group) * 16;
     const long long rv = (row0 + tok) * p.ld_v + h * 16;
     const float x_g = gate_scalar(__bfloat162float(p.b_logits[rb + g]), __bfloat162float(p.v[rv + g]));
     const float x_g8 = gate_scalar(__bfloat162float(p.b_logits[rb + g + 8]), __bfloat162float(p.v[rv + g + 8]));
@@ -115,7 +122,7 @@ struct GatedCursor {
   }
 };
 
-template <int TL, int STAGES>
+template <int TL, int STAGES, bool SHARED>
 __global__ void __launch_bounds__(128)
 btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_out,
@@ -159,9 +166,21 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
   GatedCursor prod(work.bh, work.cs, work.step, hgs), cons(work.bh, work.cs, work.step, hgs);
   int s_prod = 0;
   auto issue = [&]() {
-    if (tid == 0) {
-      const uint32_t dst = base + s_prod * SM::kStage;
-      const uint32_t bar = bars + s_prod * 8;
+    const uint32_t dst = base + s_prod * SM::kStage;
+    const uint32_t bar = bars + s_prod * 8;
+    if constexpr (SHARED) {
+      // thread 0: the V box (the thread that also stores `out` from that buffer), threads 1-4: the B_logits tiles
+      // of heads 0-3, threads 5-8: their C tiles; one copy instruction for all nine.  The byte count is the same
+      // as for three full boxes.
+      if (tid < 9) {
+        if (tid == 0) mbar_arrive_expect_tx(bar, 3 * kGatedBox);
+        const int t = tid - 1, w = t & 3;
+        const int kv_col = ((prod.hg * 4 + w) / p.group) * 16;
+        const uint64_t map = reinterpret_cast<uint64_t>(tid == 0 ? &tm_v : (t < 4 ? &tm_b : &tm_c));
+        const uint32_t to = tid == 0 ? dst + 2 * kGatedBox : dst + (t >> 2) * kGatedBox + w * (TL * 32);
+        tma_load_3d(to, map, tid == 0 ? prod.hg * 64 : kv_col, prod.cs * TL, prod.b, bar);
+      }
+    } else if (tid == 0) {
       mbar_arrive_expect_tx(bar, 3 * kGatedBox);
       tma_load_3d(dst, &tm_b, prod.hg * 64, prod.cs * TL, prod.b, bar);
       tma_load_3d(dst + kGatedBox, &tm_c, prod.hg * 64, prod.cs * TL, prod.b, bar);
@@ -195,6 +214,9 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
 
   // lane-constant addressing of this warp's [16 tokens][16 channels] block inside a box (see the header)
   const uint32_t frag_off = ((lane & 7) + 8 * (lane >> 4)) * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
+  // the same block inside this warp's dense [TL][16 channels] tile of a shared key/value head
+  const uint32_t kv_off = SHARED ? warp * (TL * 32) + ((lane & 7) + 8 * (lane >> 4)) * 32 + ((lane >> 3) & 1) * 16 : frag_off;
+  constexpr uint32_t kKvBlock = SHARED ? 512 : 2048;  // bytes from one 16-token block to the next
   float cg = 0.0f, cg8 = 0.0f;
   int s = 0;
   uint32_t phase = 0;
@@ -215,7 +237,7 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
       load_logits(peek, zn2);
       peek.next(ncs, hgs);
     }
-    const bool ok = mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);
+    const bool ok = mbar_wait_bounded(bars + s * 8, phase, p.wait_limit_ns);
     if (__syncthreads_or(!ok)) {
       failed = true;
       break;
@@ -231,16 +253,16 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
     }
     const float* tg = tab + tl.g;
     const float* tt = tab + 2 * tl.t;
-    const uint32_t sb = base + s * SM::kStage + frag_off;
+    const uint32_t sb = base + s * SM::kStage + kv_off;
     const uint32_t sc = sb + kGatedBox;
-    const uint32_t sv = sb + 2 * kGatedBox;
+    const uint32_t sv = base + s * SM::kStage + 2 * kGatedBox + frag_off;
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
       if (i < nt) {
         uint32_t bf[4], vf[4], cf[4];
-        ldmatrix_x4_trans(sb + 2048 * i, bf[0], bf[1], bf[2], bf[3]);
+        ldmatrix_x4_trans(sb + kKvBlock * i, bf[0], bf[1], bf[2], bf[3]);
         ldmatrix_x4_trans(sv + 2048 * i, vf[0], vf[1], vf[2], vf[3]);
-        ldmatrix_x4_trans(sc + 2048 * i, cf[0], cf[1], cf[2], cf[3]);
+        ldmatrix_x4_trans(sc + kKvBlock * i, cf[0], cf[1], cf[2], cf[3]);
         const uint32_t x0 = gate_pair(bf[0], vf[0]), x1 = gate_pair(bf[1], vf[1]);
         const uint32_t x2 = gate_pair(bf[2], vf[2]), x3 = gate_pair(bf[3], vf[3]);
         LmatFrag lf, lo;
@@ -282,7 +304,7 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
   if (failed) {
     if (tid == 0) report_error(1u, warp, j);
     for (int k = j; k < n && k <= j + AHEAD; ++k) {  // let the loads in flight land before the CTA leaves
-      mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);
+      mbar_wait_bounded(bars + s * 8, phase, p.wait_limit_ns);
       if (++s == STAGES) {
         s = 0;
         phase ^= 1u;

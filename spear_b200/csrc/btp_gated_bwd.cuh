@@ -12,6 +12,11 @@
 // [32 tokens][64 channels] (B_logits, C, V, dOut).  dB, dC, dV overwrite their inputs in shared memory and
 // leave with TMA stores.  As in the plain backward kernel, a block is finished one block later (it needs
 // the gradient that its right neighbour sends), so a block's operands and accumulators wait in registers.
+//
+// Shared key/value heads (SHARED == true): B_logits and C are [B, L, kv_heads*16] and are read in place, each
+// warp fetching its key/value head's 16 columns as a dense tile of its own (see btp_gated.cuh).  dB_logits and
+// dC are still produced PER HEAD, [B, L, H*16] (the tile a warp loaded is the tile it overwrites); the caller
+// sums them over the heads of a group, which is the one reduction autograd would do anyway.
 #pragma once
 
 #include "btp_gated.cuh"
@@ -27,6 +32,8 @@ struct GatedBwdParams {
   __nv_bfloat16* da_logits;
   long long ld_a, ld_b, ld_c, ld_v, ld_do, ld_da;  // row pitches in elements
   int L, H, hgs, ncs, total_units, use_carry, interleave;
+  int group;  // heads per key/value head (see btp_gated.cuh); 1 when every head has its own
+  unsigned long long wait_limit_ns;  // bounded waits give up after this long
 };
 
 constexpr int kGbTL = 32;            // tokens per chunk
@@ -61,7 +68,7 @@ __device__ __forceinline__ void gated_halo_right(const GatedBwdParams& p, long l
     const int tok = 2 * t + (j & 1) + ((j >> 1) << 3);
     const float w = lmat_weight<true>(ex2(__shfl_sync(0xffffffffu, T, tok) - T0));
     const long long rd = (row0 + tok) * p.ld_do + h * 16;
-    const long long rc = (row0 + tok) * p.ld_c + h * 16;
+    const long long rc = (row0 + tok) * p.ld_c + (h / p.group) * 16;
     const float dy_g = round_bf16(__bfloat162float(p.dout[rd + g]) * __bfloat162float(p.c[rc + g]));
     const float dy_g8 = round_bf16(__bfloat162float(p.dout[rd + g + 8]) * __bfloat162float(p.c[rc + g + 8]));
     sg = fmaf(dy_g, w, sg);
@@ -85,7 +92,7 @@ struct GatedPending {
   uint32_t df[4];      // dOut
 };
 
-template <int STAGES>
+template <int STAGES, bool SHARED>
 __global__ void __launch_bounds__(128, 4)
 btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -127,7 +134,18 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
   GatedCursor prod(work.bh, work.cs, work.step, hgs), cons(work.bh, work.cs, work.step, hgs);
   int s_prod = 0, d_prod = 0, issued = 0;
   auto issue = [&]() {
-    if (tid == 0) {
+    if constexpr (SHARED) {
+      // threads 0-3: B_logits tiles of heads 0-3, 4-7: their C tiles, 8: V box, 9: dOut box; one copy instruction
+      if (tid < 10) {
+        const uint32_t bar = bars + s_prod * 8;
+        if (tid == 0) mbar_arrive_expect_tx(bar, 4 * kGbBox);
+        const int w = tid & 3;
+        const int kv_col = ((prod.hg * 4 + w) / p.group) * 16;
+        const uint64_t map = reinterpret_cast<uint64_t>(tid < 4 ? &tm_b : (tid < 8 ? &tm_c : (tid == 8 ? &tm_v : &tm_do)));
+        const uint32_t to = tid < 8 ? io_addr(tid >> 2, s_prod) + w * (TL * 32) : (tid == 8 ? io_addr(2, s_prod) : do_addr(d_prod));
+        tma_load_3d(to, map, tid < 8 ? kv_col : prod.hg * 64, prod.cs * TL, prod.b, bar);
+      }
+    } else if (tid == 0) {
       const uint32_t bar = bars + s_prod * 8;
       const int col = prod.hg * 64, row = prod.cs * TL;
       mbar_arrive_expect_tx(bar, 4 * kGbBox);
@@ -157,6 +175,9 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
   }
 
   const uint32_t frag_off = ((lane & 7) + 8 * (lane >> 4)) * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
+  // the same block inside this warp's dense [TL][16 channels] tile (shared key/value heads)
+  const uint32_t kv_off = SHARED ? warp * (TL * 32) + ((lane & 7) + 8 * (lane >> 4)) * 32 + ((lane >> 3) & 1) * 16 : frag_off;
+  constexpr uint32_t kKvBlock = SHARED ? 512 : 2048;  // bytes from one 16-token block to the next in the B / C tiles
 
   // ---- per chunk: tables T, P, Pshift, L15, S (one token per lane, 16 lanes per block)
   auto make_tables = [&](float z, float* tab) {
@@ -185,9 +206,9 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
   auto front = [&](const float* tab, uint32_t sb, uint32_t sc, uint32_t sv, uint32_t sd, int i, float cg, float cg8,
                    GatedPending& pd, float& dc_g, float& dc_g8) {
     uint32_t bf[4], cf[4];
-    ldmatrix_x4_trans(sb + 2048 * i, bf[0], bf[1], bf[2], bf[3]);
+    ldmatrix_x4_trans(sb + kKvBlock * i, bf[0], bf[1], bf[2], bf[3]);
     ldmatrix_x4_trans(sv + 2048 * i, pd.vf[0], pd.vf[1], pd.vf[2], pd.vf[3]);
-    ldmatrix_x4_trans(sc + 2048 * i, cf[0], cf[1], cf[2], cf[3]);
+    ldmatrix_x4_trans(sc + kKvBlock * i, cf[0], cf[1], cf[2], cf[3]);
     ldmatrix_x4_trans(sd + 2048 * i, pd.df[0], pd.df[1], pd.df[2], pd.df[3]);
     uint32_t x[4], dy[4];
 #pragma unroll
@@ -216,7 +237,7 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
     const uint32_t q2 = pack_bf16x2(bf16_lo(pd.df[2]) * fmaf(Pb.x, cg, pd.v1[0]), bf16_hi(pd.df[2]) * fmaf(Pb.y, cg, pd.v1[1]));
     const uint32_t q3 = pack_bf16x2(bf16_lo(pd.df[3]) * fmaf(Pb.x, cg8, pd.v1[2]), bf16_hi(pd.df[3]) * fmaf(Pb.y, cg8, pd.v1[3]));
     __syncwarp();  // every lane holds its C fragment before the block is overwritten
-    stmatrix_x4_trans(sc + 2048 * i, q0, q1, q2, q3);
+    stmatrix_x4_trans(sc + kKvBlock * i, q0, q1, q2, q3);
     // gradient this block sends to its left neighbour: P[0] * gw[:,0]
     const float p_first = tab[TL + 16 * i];
     dc_g = p_first * __shfl_sync(0xffffffffu, pd.g0[0], lane & ~3);
@@ -291,7 +312,18 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
   auto flush = [&]() {
     fence_proxy_async_smem();
     __syncthreads();
-    if (tid == 0) {
+    if constexpr (SHARED) {
+      // threads 0-3: the per-head dB tiles, 4-7: the per-head dC tiles (16 columns each of the [B, L, H*16]
+      // outputs), 8: the dV box; every storing thread keeps its own async group
+      if (tid < 9) {
+        const int w = tid & 3;
+        const uint64_t map = reinterpret_cast<uint64_t>(tid < 4 ? &tm_db : (tid < 8 ? &tm_dc : &tm_dv));
+        const uint32_t from = tid < 8 ? io_addr(tid >> 2, p_stage) + w * (TL * 32) : io_addr(2, p_stage);
+        tma_store_3d(map, tid < 8 ? (p_hg * 4 + w) * 16 : p_hg * 64, p_c0, p_b, from);
+        bulk_commit_group();
+        if (issued < n) bulk_wait_group_read<1>();
+      }
+    } else if (tid == 0) {
       tma_store_3d(&tm_db, p_hg * 64, p_c0, p_b, io_addr(0, p_stage));
       tma_store_3d(&tm_dc, p_hg * 64, p_c0, p_b, io_addr(1, p_stage));
       tma_store_3d(&tm_dv, p_hg * 64, p_c0, p_b, io_addr(2, p_stage));
@@ -314,7 +346,7 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
       z_after = load_logit(peek);
       peek.next(ncs, hgs);
     }
-    const bool ok = mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);
+    const bool ok = mbar_wait_bounded(bars + s * 8, phase, p.wait_limit_ns);
     if (__syncthreads_or(!ok)) {
       failed = true;
       break;
@@ -326,12 +358,12 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
     if (j == 0 && cons.cs != 0 && p.use_carry) {
       GatedParams hp{};
       hp.a_logits = p.a_logits; hp.b_logits = p.b_logits; hp.v = p.v;
-      hp.ld_a = p.ld_a; hp.ld_b = p.ld_b; hp.ld_v = p.ld_v; hp.L = L;
+      hp.ld_a = p.ld_a; hp.ld_b = p.ld_b; hp.ld_v = p.ld_v; hp.L = L; hp.group = p.group;
       gated_halo_left(hp, cons.b, cons.hg * 4 + warp, c0 - 16, lane, vl_g, vl_g8);
     }
     const float* tt = tab + 2 * tl.t;
     __nv_bfloat16* da = da_stage + tset * TL * 4;
-    const uint32_t sb = io_addr(0, s) + frag_off, sc = io_addr(1, s) + frag_off, sv = io_addr(2, s) + frag_off;
+    const uint32_t sb = io_addr(0, s) + kv_off, sc = io_addr(1, s) + kv_off, sv = io_addr(2, s) + frag_off;
     const uint32_t sd = do_addr(d) + frag_off;
     const bool seq_first = (cons.cs == 0);
 #pragma unroll
@@ -362,7 +394,7 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
     p_seq_end = (cons.cs == ncs - 1);
     p_tt = tt + 16 * (nt - 1);
     p_da = da + 16 * (nt - 1) * 4;
-    p_sb = sb + 2048 * (nt - 1);
+    p_sb = sb + kKvBlock * (nt - 1);
     p_sv = sv + 2048 * (nt - 1);
     p_stage = s;
     p_set = tset;
@@ -390,14 +422,14 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
   if (failed) {
     if (tid == 0) report_error(1u, warp, j);
     for (int k = j; k < issued; ++k) {
-      mbar_wait_bounded(bars + s * 8, phase, kWaitLimitNs);
+      mbar_wait_bounded(bars + s * 8, phase, p.wait_limit_ns);
       if (++s == STAGES) {
         s = 0;
         phase ^= 1u;
       }
     }
   }
-  if (tid == 0) bulk_wait_group<0>();
+  if (tid < (SHARED ? 9 : 1)) bulk_wait_group<0>();
 }
 
 }  // namespace btp

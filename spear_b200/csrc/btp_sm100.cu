@@ -113,16 +113,19 @@ int make_map(CUtensorMap* map, const void* base, MapShape sh, long long rows, in
 }
 
 // Token-major tensor [B][L][cols] bf16 with row pitch `ld` elements; box = `box_rows` tokens x 64 channels.
-int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, long long ld, int box_rows = 64) {
+// `narrow`: box = `box_rows` tokens x 16 channels (one head), dense 32-byte rows without swizzle - the per-head
+// tiles of the kernels that read shared key/value heads in place.
+int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, long long ld, int box_rows = 64,
+                    bool narrow = false) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(ld) * 2 * L};
-  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
+  const cuuint32_t box[3] = {narrow ? 16u : 64u, static_cast<cuuint32_t>(box_rows), 1u};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, narrow ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
   return BTP_OK;
 }
@@ -380,10 +383,10 @@ int backward_variant(const void* coeff, const void* x, const void* dy, void* dx,
 }
 
 // ------------------------------------------------------------------ gated forward launch
-template <int TL, int STAGES>
+template <int TL, int STAGES, bool SHARED>
 int launch_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out, int B, int L,
-                         int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_out, int k,
-                         void* stream) {
+                         int H, int kv_heads, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
+                         long long ld_out, int k, void* stream) {
   const char* fn = "btp_sm100_gated_forward";
   const long long cols = static_cast<long long>(H) * 16;
   const int hgs = H / 4;
@@ -391,7 +394,7 @@ int launch_gated_forward(const void* a_logits, const void* b_logits, const void*
   const long long total = static_cast<long long>(B) * hgs * ncs;
   if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
   using SM = GatedSmem<TL, STAGES>;
-  auto kern = btp_gated_forward_kernel<TL, STAGES>;
+  auto kern = btp_gated_forward_kernel<TL, STAGES, SHARED>;
   static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
   int dev;
   DeviceInfo info;
@@ -400,8 +403,9 @@ int launch_gated_forward(const void* a_logits, const void* b_logits, const void*
   int ctas;
   if ((rc = LN.prepare(dev, &ctas))) return rc;
   CUtensorMap tm_b, tm_c, tm_v, tm_o;
-  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, static_cast<int>(cols), ld_b, TL))) return rc;
-  if ((rc = make_map_tokens(&tm_c, c, B, L, static_cast<int>(cols), ld_c, TL))) return rc;
+  const int kv_cols = kv_heads * 16;
+  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, SHARED ? kv_cols : static_cast<int>(cols), ld_b, TL, SHARED))) return rc;
+  if ((rc = make_map_tokens(&tm_c, c, B, L, SHARED ? kv_cols : static_cast<int>(cols), ld_c, TL, SHARED))) return rc;
   if ((rc = make_map_tokens(&tm_v, v, B, L, static_cast<int>(cols), ld_v, TL))) return rc;
   if ((rc = make_map_tokens(&tm_o, out, B, L, static_cast<int>(cols), ld_out, TL))) return rc;
   const long long cap = static_cast<long long>(info.sms) * ctas;
@@ -413,8 +417,63 @@ int launch_gated_forward(const void* a_logits, const void* b_logits, const void*
   p.ld_a = ld_a; p.ld_b = ld_b; p.ld_v = ld_v;
   p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
   p.use_carry = (k == 2);
+  p.group = H / kv_heads;
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
   kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_o, p);
+  BTP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BTP_OK;
+}
+
+// ------------------------------------------------------------------ gated backward launch
+template <bool SHARED>
+int launch_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
+                          void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, int kv_heads,
+                          long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_do, long long ld_da,
+                          long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream) {
+  const char* fn = "btp_sm100_gated_backward";
+  const long long cols = static_cast<long long>(H) * 16;
+  const int hgs = H / 4;
+  const int ncs = (L + kGbTL - 1) / kGbTL;
+  const long long total = static_cast<long long>(B) * hgs * ncs;
+  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
+  constexpr int STAGES = 3;
+  using SM = GatedBwdSmem<STAGES>;
+  auto kern = btp_gated_backward_kernel<STAGES, SHARED>;
+  static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = LN.prepare(dev, &ctas))) return rc;
+  CUtensorMap tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv;
+  const int icols = static_cast<int>(cols), kcols = kv_heads * 16;
+  // shared key/value heads: B_logits and C are read, and dB_logits / dC written, as per-head 16-column tiles
+  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, SHARED ? kcols : icols, ld_b, kGbTL, SHARED))) return rc;
+  if ((rc = make_map_tokens(&tm_c, c, B, L, SHARED ? kcols : icols, ld_c, kGbTL, SHARED))) return rc;
+  if ((rc = make_map_tokens(&tm_v, v, B, L, icols, ld_v, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_do, dout, B, L, icols, ld_do, kGbTL))) return rc;
+  if ((rc = make_map_tokens(&tm_db, db_logits, B, L, icols, ld_db, kGbTL, SHARED))) return rc;
+  if ((rc = make_map_tokens(&tm_dc, dc, B, L, icols, ld_dc, kGbTL, SHARED))) return rc;
+  if ((rc = make_map_tokens(&tm_dv, dv, B, L, icols, ld_dv, kGbTL))) return rc;
+  const long long cap = static_cast<long long>(info.sms) * ctas;
+  const int grid = static_cast<int>(total < cap ? total : cap);
+  GatedBwdParams p{};
+  p.a_logits = static_cast<const __nv_bfloat16*>(a_logits);
+  p.b_logits = static_cast<const __nv_bfloat16*>(b_logits);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.dout = static_cast<const __nv_bfloat16*>(dout);
+  p.da_logits = static_cast<__nv_bfloat16*>(da_logits);
+  p.ld_a = ld_a; p.ld_b = ld_b; p.ld_c = ld_c; p.ld_v = ld_v; p.ld_do = ld_do; p.ld_da = ld_da;
+  p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
+  p.use_carry = (k == 2);
+  p.group = H / kv_heads;
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
+  kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv, p);
   BTP_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
@@ -547,7 +606,7 @@ int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, 
 }
 
 int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out, int B,
-                            int L, int H, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
+                            int L, int H, int kv_heads, long long ld_a, long long ld_b, long long ld_c, long long ld_v,
                             long long ld_out, int k, void* stream) {
   const char* fn = "btp_sm100_gated_forward";
   if (B <= 0 || H <= 0 || L <= 0) return fail(BTP_ERR_BAD_SHAPE, "%s: B, L, H must be positive (got %d, %d, %d)", fn, B, L, H);
@@ -555,8 +614,10 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
   if (H % 4 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: the number of heads must be a multiple of 4 (got %d)", fn, H);
   if (k != 1 && k != 2) return fail(BTP_ERR_BAD_ORDER, "%s: k must be 1 or 2 (got %d)", fn, k);
   if (!a_logits || !b_logits || !c || !v || !out) return fail(BTP_ERR_NULL_POINTER, "%s: no pointer may be NULL", fn);
-  const long long cols = static_cast<long long>(H) * 16;
-  if (ld_a < H || ld_b < cols || ld_c < cols || ld_v < cols || ld_out < cols)
+  if (kv_heads <= 0 || H % kv_heads != 0)
+    return fail(BTP_ERR_BAD_SHAPE, "%s: kv_heads must divide the number of heads (got %d, %d)", fn, kv_heads, H);
+  const long long cols = static_cast<long long>(H) * 16, kcols = static_cast<long long>(kv_heads) * 16;
+  if (ld_a < H || ld_b < kcols || ld_c < kcols || ld_v < cols || ld_out < cols)
     return fail(BTP_ERR_BAD_SHAPE, "%s: a row pitch is smaller than its row", fn);
   if (ld_b % 8 || ld_c % 8 || ld_v % 8 || ld_out % 8)
     return fail(BTP_ERR_MISALIGNED, "%s: row pitches of B_logits, C, V and out must be multiples of 8 elements", fn);
@@ -570,15 +631,18 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
   const int rc = device_info(&dev, &info);
   if (rc) return rc;
   const long long head_groups = static_cast<long long>(B) * (H / 4);
-  if (L <= 512 && head_groups >= 3ll * 6 * info.sms)
-    return launch_gated_forward<32, 3>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
-  return launch_gated_forward<64, 3>(a_logits, b_logits, c, v, out, B, L, H, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
+  const bool small = L <= 512 && head_groups >= 3ll * 6 * info.sms;
+  if (kv_heads < H)
+    return small ? launch_gated_forward<32, 3, true>(a_logits, b_logits, c, v, out, B, L, H, kv_heads, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream)
+                 : launch_gated_forward<64, 3, true>(a_logits, b_logits, c, v, out, B, L, H, kv_heads, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
+  return small ? launch_gated_forward<32, 3, false>(a_logits, b_logits, c, v, out, B, L, H, kv_heads, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream)
+               : launch_gated_forward<64, 3, false>(a_logits, b_logits, c, v, out, B, L, H, kv_heads, ld_a, ld_b, ld_c, ld_v, ld_out, k, stream);
 }
 
 int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
-                             void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, long long ld_a,
-                             long long ld_b, long long ld_c, long long ld_v, long long ld_do, long long ld_da,
-                             long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream) {
+                             void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, int kv_heads,
+                             long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_do,
+                             long long ld_da, long long ld_db, long long ld_dc, long long ld_dv, int k, void* stream) {
   const char* fn = "btp_sm100_gated_backward";
   if (B <= 0 || H <= 0 || L <= 0) return fail(BTP_ERR_BAD_SHAPE, "%s: B, L, H must be positive (got %d, %d, %d)", fn, B, L, H);
   if (L % 16 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: L must be a multiple of 16 (got %d)", fn, L);
@@ -586,8 +650,10 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
   if (k != 1 && k != 2) return fail(BTP_ERR_BAD_ORDER, "%s: k must be 1 or 2 (got %d)", fn, k);
   if (!a_logits || !b_logits || !c || !v || !dout || !da_logits || !db_logits || !dc || !dv)
     return fail(BTP_ERR_NULL_POINTER, "%s: no pointer may be NULL", fn);
-  const long long cols = static_cast<long long>(H) * 16;
-  if (ld_a < H || ld_da < H || ld_b < cols || ld_c < cols || ld_v < cols || ld_do < cols || ld_db < cols || ld_dc < cols ||
+  if (kv_heads <= 0 || H % kv_heads != 0)
+    return fail(BTP_ERR_BAD_SHAPE, "%s: kv_heads must divide the number of heads (got %d, %d)", fn, kv_heads, H);
+  const long long cols = static_cast<long long>(H) * 16, kcols = static_cast<long long>(kv_heads) * 16;
+  if (ld_a < H || ld_da < H || ld_b < kcols || ld_c < kcols || ld_v < cols || ld_do < cols || ld_db < cols || ld_dc < cols ||
       ld_dv < cols)
     return fail(BTP_ERR_BAD_SHAPE, "%s: a row pitch is smaller than its row", fn);
   if (ld_b % 8 || ld_c % 8 || ld_v % 8 || ld_do % 8 || ld_db % 8 || ld_dc % 8 || ld_dv % 8 || ld_da % 4)
@@ -595,46 +661,11 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
   if (misaligned(b_logits) || misaligned(c) || misaligned(v) || misaligned(dout) || misaligned(db_logits) || misaligned(dc) ||
       misaligned(dv) || (reinterpret_cast<uintptr_t>(a_logits) & 1u) || (reinterpret_cast<uintptr_t>(da_logits) & 7u))
     return fail(BTP_ERR_MISALIGNED, "%s: the [B,L,H*16] tensors must be 16-byte aligned, dA_logits 8-byte aligned", fn);
-  const int hgs = H / 4;
-  const int ncs = (L + kGbTL - 1) / kGbTL;
-  const long long total = static_cast<long long>(B) * hgs * ncs;
-  if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
-  constexpr int STAGES = 3;
-  using SM = GatedBwdSmem<STAGES>;
-  auto kern = btp_gated_backward_kernel<STAGES>;
-  static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
-  int dev;
-  DeviceInfo info;
-  int rc = device_info(&dev, &info);
-  if (rc) return rc;
-  int ctas;
-  if ((rc = LN.prepare(dev, &ctas))) return rc;
-  CUtensorMap tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv;
-  const int icols = static_cast<int>(cols);
-  if ((rc = make_map_tokens(&tm_b, b_logits, B, L, icols, ld_b, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_c, c, B, L, icols, ld_c, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_v, v, B, L, icols, ld_v, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_do, dout, B, L, icols, ld_do, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_db, db_logits, B, L, icols, ld_db, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_dc, dc, B, L, icols, ld_dc, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_dv, dv, B, L, icols, ld_dv, kGbTL))) return rc;
-  const long long cap = static_cast<long long>(info.sms) * ctas;
-  const int grid = static_cast<int>(total < cap ? total : cap);
-  GatedBwdParams p{};
-  p.a_logits = static_cast<const __nv_bfloat16*>(a_logits);
-  p.b_logits = static_cast<const __nv_bfloat16*>(b_logits);
-  p.c = static_cast<const __nv_bfloat16*>(c);
-  p.v = static_cast<const __nv_bfloat16*>(v);
-  p.dout = static_cast<const __nv_bfloat16*>(dout);
-  p.da_logits = static_cast<__nv_bfloat16*>(da_logits);
-  p.ld_a = ld_a; p.ld_b = ld_b; p.ld_c = ld_c; p.ld_v = ld_v; p.ld_do = ld_do; p.ld_da = ld_da;
-  p.L = L; p.H = H; p.hgs = hgs; p.ncs = ncs; p.total_units = static_cast<int>(total);
-  p.use_carry = (k == 2);
-  p.interleave = static_cast<long long>(B) * hgs >= 3ll * grid;  // enough sequences to deal them out whole
-  kern<<<grid, 128, SM::kBytes, static_cast<cudaStream_t>(stream)>>>(tm_b, tm_c, tm_v, tm_do, tm_db, tm_dc, tm_dv, p);
-  BTP_CUDA_TRY(cudaGetLastError());
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return BTP_OK;
+  if (kv_heads < H)
+    return launch_gated_backward<true>(a_logits, b_logits, c, v, dout, da_logits, db_logits, dc, dv, B, L, H, kv_heads, ld_a,
+                                       ld_b, ld_c, ld_v, ld_do, ld_da, ld_db, ld_dc, ld_dv, k, stream);
+  return launch_gated_backward<false>(a_logits, b_logits, c, v, dout, da_logits, db_logits, dc, dv, B, L, H, kv_heads, ld_a,
+                                      ld_b, ld_c, ld_v, ld_do, ld_da, ld_db, ld_dc, ld_dv, k, stream);
 }
 
 int btp_sm100_decode_step(const void* a_t, const void* x_t, const void* c_t, const void* v_t, void* y_t,

@@ -104,6 +104,72 @@ class SigmoidA(nn.Module):
         return A, X, C, V
 
 
+class _PackedProjections:
+    """The four projection weights of SigmoidA (swr.py:157-164) as row slices of ONE [3*dim + heads, dim] matrix,
+    and their biases as slices of one vector, so that the projections run as one GEMM without concatenating
+    anything per call.
+
+    The parameters stay what they are - the same nn.Parameter objects under the same names, so state_dict,
+    load_state_dict and optimizers see no difference - but their storage is moved into the packed buffers:
+    `p.data` becomes a view of the packed matrix.  In-place updates (optimizer steps, load_state_dict) then
+    change the packed matrix directly.  Operations that give a parameter fresh storage (`.to()`, `.cuda()`,
+    a dtype cast) break the link; `current()` notices (the view's address no longer lies in the buffer) and packs
+    again.  Row order: proj_b | proj_c | proj_v | proj_a, the column order the gated kernel reads.
+    """
+
+    def __init__(self, prm: "SigmoidA"):
+        self.weights = (prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight)
+        self.biases = (prm.proj_b.bias, prm.proj_c.bias, None, prm.proj_a.bias)
+        rows = [w.shape[0] for w in self.weights]
+        self.offsets = [sum(rows[:i]) for i in range(5)]
+        with torch.no_grad():
+            self.weight = torch.cat([w.detach() for w in self.weights], dim=0)
+            self.bias = torch.zeros(self.offsets[4], device=self.weight.device, dtype=self.weight.dtype)
+            for i, (w, b) in enumerate(zip(self.weights, self.biases)):
+                lo, hi = self.offsets[i], self.offsets[i + 1]
+                w.data = self.weight[lo:hi]
+                if b is not None:
+                    self.bias[lo:hi] = b.detach()
+                    b.data = self.bias[lo:hi]
+
+    def intact(self, prm: "SigmoidA") -> bool:
+        ws = (prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight)
+        bs = (prm.proj_b.bias, prm.proj_c.bias, None, prm.proj_a.bias)
+        if any(a is not b for a, b in zip(ws + bs, self.weights + self.biases)):
+            return False
+        esz, dim = self.weight.element_size(), self.weight.shape[1]
+        for i, (w, b) in enumerate(zip(ws, bs)):
+            if w.dtype != self.weight.dtype or w.device != self.weight.device:
+                return False
+            if w.data_ptr() != self.weight.data_ptr() + self.offsets[i] * dim * esz:
+                return False
+            if b is not None and b.data_ptr() != self.bias.data_ptr() + self.offsets[i] * esz:
+                return False
+        return True
+
+
+class _WideProjection(torch.autograd.Function):
+    """wide = u @ W^T + bias with W, bias the packed buffers; the gradient of W is formed by ONE GEMM and handed
+    to the four parameters as its row slices."""
+
+    @staticmethod
+    def forward(ctx, u, weight, bias, offsets, w_b, w_c, w_v, w_a, b_b, b_c, b_a):
+        ctx.save_for_backward(u, weight)
+        ctx.offsets = offsets
+        return nn.functional.linear(u, weight, bias)
+
+    @staticmethod
+    def backward(ctx, dwide):
+        u, weight = ctx.saved_tensors
+        o = ctx.offsets
+        d2 = dwide.reshape(-1, dwide.shape[-1])
+        du = (d2 @ weight).reshape(u.shape) if ctx.needs_input_grad[0] else None
+        dw = d2.t() @ u.reshape(-1, u.shape[-1])
+        db = d2.sum(dim=0)
+        return (du, None, None, None, dw[o[0]:o[1]], dw[o[1]:o[2]], dw[o[2]:o[3]], dw[o[3]:o[4]],
+                db[o[0]:o[1]], db[o[1]:o[2]], db[o[3]:o[4]])
+
+
 class Phalanx(nn.Module):
     """Drop-in for spear.nn.phalanx.Phalanx (swr.py:224-331) running the sm_100a BTP kernels."""
 
@@ -163,6 +229,7 @@ class Phalanx(nn.Module):
         # With fused gating and heads % 8 == 0 the four projections (swr.py:157-175) run as ONE GEMM whose
         # output columns (b | c | v | a) the gated kernel reads in place; the parameters stay separate.
         self.fused_projection = True
+        self._packed = None  # _PackedProjections, built on the first fused forward
 
     def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
         from spear_b200.ops.btp.gated import gated_btp, gated_btp_wide
@@ -171,20 +238,22 @@ class Phalanx(nn.Module):
         prm = self.param
         if self.kv_heads < self.heads:
             # Heads share key/value heads (KVRepeat, swr.py:96-103: head h reads key/value head h // group): the
-            # two shared tensors are repeated to all heads in one copy each, and autograd sums their gradients
-            # over the group; everything else stays fused.
-            batch, length, _ = u.shape
-            group = self.heads // self.kv_heads
-
-            def repeat(t):
-                t = t.view(batch, length, self.kv_heads, 1, self.head_dim)
-                return t.expand(batch, length, self.kv_heads, group, self.head_dim).reshape(batch, length, self.dim)
-
-            y = gated_btp(prm.proj_a(u), repeat(prm.proj_b(u)), repeat(prm.proj_c(u)), prm.proj_v(u), self.k)
+            # gated kernels read the narrow B_logits and C in place, nothing is repeated.
+            y = gated_btp(prm.proj_a(u), prm.proj_b(u), prm.proj_c(u), prm.proj_v(u), self.k)
         elif self.fused_projection and self.heads % 8 == 0:
-            weight = torch.cat([prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight], dim=0)
-            bias = torch.cat([prm.proj_b.bias, prm.proj_c.bias, torch.zeros_like(prm.proj_b.bias), prm.proj_a.bias])
-            y = gated_btp_wide(nn.functional.linear(u, weight, bias), self.heads, self.k)
+            if torch.compiler.is_compiling():
+                # under torch.compile the concatenation is traced (and fused) like any other op
+                weight = torch.cat([prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight], dim=0)
+                bias = torch.cat([prm.proj_b.bias, prm.proj_c.bias, torch.zeros_like(prm.proj_b.bias), prm.proj_a.bias])
+                wide = nn.functional.linear(u, weight, bias)
+            else:
+                pk = self._packed
+                if pk is None or not pk.intact(prm):
+                    pk = self._packed = _PackedProjections(prm)
+                wide = _WideProjection.apply(u, pk.weight, pk.bias, pk.offsets, prm.proj_b.weight, prm.proj_c.weight,
+                                             prm.proj_v.weight, prm.proj_a.weight, prm.proj_b.bias, prm.proj_c.bias,
+                                             prm.proj_a.bias)
+            y = gated_btp_wide(wide, self.heads, self.k)
         else:
             y = gated_btp(prm.proj_a(u), prm.proj_b(u), prm.proj_c(u), prm.proj_v(u), self.k)
         return self.proj_out(y)

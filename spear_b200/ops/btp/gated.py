@@ -21,8 +21,9 @@ __all__ = ["gated_btp", "gated_btp_wide", "gated_btp_supported"]
 
 
 def gated_btp_supported(heads: int, kv_heads: int, length: int) -> bool:
-    """The fused kernels take 4 heads per CTA and per-head B_logits and C; a layer whose heads share key/value
-    heads (kv_heads < heads) repeats those two tensors to all heads first (see Phalanx._forward_fused)."""
+    """The fused kernels take 4 heads per CTA.  Heads that share key/value heads (kv_heads < heads, KVRepeat of
+    spear/nn/phalanx/swr.py:96-103) are supported for any divisor: the kernels read the shared B_logits and C
+    columns in place."""
     return heads % 4 == 0 and heads % kv_heads == 0 and length % 16 == 0
 
 
@@ -50,16 +51,28 @@ def _same_batch_and_length(a_logits: torch.Tensor, others) -> None:
             raise ValueError(f"{name} is on {t.device}, a_logits on {a_logits.device}")
 
 
+def _kv_heads(b_logits: torch.Tensor, c: torch.Tensor, H: int) -> int:
+    """Number of key/value heads from the width of B_logits (C must agree); a divisor of H."""
+    if b_logits.dim() != 3 or c.dim() != 3 or b_logits.shape[2] != c.shape[2]:
+        raise ValueError(f"b_logits and c must be [B, L, kv_heads*16] of one width, got {tuple(b_logits.shape)}, {tuple(c.shape)}")
+    kv, rest = divmod(b_logits.shape[2], 16)
+    if rest or kv < 1 or H % kv:
+        raise ValueError(f"b_logits has {b_logits.shape[2]} columns: not 16 per key/value head with kv_heads dividing {H} heads")
+    return kv
+
+
 def _launch_forward(a_logits, b_logits, c, v, out, k: int) -> None:
     _same_batch_and_length(a_logits, ((b_logits, "b_logits"), (c, "c"), (v, "v"), (out, "out")))
     B, L, H = a_logits.shape
     cols = H * 16
+    kv = _kv_heads(b_logits, c, H)
     ld_a = _rows(a_logits, H, "a_logits")
-    ld_b, ld_c, ld_v, ld_o = (_rows(t, cols, n) for t, n in ((b_logits, "b_logits"), (c, "c"), (v, "v"), (out, "out")))
+    ld_b, ld_c = _rows(b_logits, kv * 16, "b_logits"), _rows(c, kv * 16, "c")
+    ld_v, ld_o = _rows(v, cols, "v"), _rows(out, cols, "out")
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     with _native._OnDevice(v.device.index) as stream:
-        rc = _lib.load().btp_sm100_gated_forward(p(a_logits), p(b_logits), p(c), p(v), p(out), B, L, H, ld_a, ld_b, ld_c,
-                                                 ld_v, ld_o, int(k), ctypes.c_void_p(stream))
+        rc = _lib.load().btp_sm100_gated_forward(p(a_logits), p(b_logits), p(c), p(v), p(out), B, L, H, kv, ld_a, ld_b,
+                                                 ld_c, ld_v, ld_o, int(k), ctypes.c_void_p(stream))
     _lib.check(rc, "btp_sm100_gated_forward")
 
 
@@ -83,13 +96,15 @@ def _launch_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, k: int) -> 
                                       (db, "db_logits"), (dc, "dc"), (dv, "dv")))
     B, L, H = a_logits.shape
     cols = H * 16
-    ld = [_rows(a_logits, H, "a_logits")] + [_rows(t, cols, n) for t, n in
-                                             ((b_logits, "b_logits"), (c, "c"), (v, "v"), (dout, "dout"))]
+    kv = _kv_heads(b_logits, c, H)
+    ld = [_rows(a_logits, H, "a_logits"), _rows(b_logits, kv * 16, "b_logits"), _rows(c, kv * 16, "c"),
+          _rows(v, cols, "v"), _rows(dout, cols, "dout")]
+    # db and dc are per head even when the inputs are shared: the caller sums them over the heads of a group
     ld += [_rows(da, H, "da_logits")] + [_rows(t, cols, n) for t, n in ((db, "db_logits"), (dc, "dc"), (dv, "dv"))]
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     with _native._OnDevice(v.device.index) as stream:
         rc = _lib.load().btp_sm100_gated_backward(p(a_logits), p(b_logits), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
-                                                  B, L, H, *ld, int(k), ctypes.c_void_p(stream))
+                                                  B, L, H, kv, *ld, int(k), ctypes.c_void_p(stream))
     _lib.check(rc, "btp_sm100_gated_backward")
 
 
@@ -133,6 +148,10 @@ def _backward(a_logits, b_logits, c, v, dout, k):
     da = torch.empty(B, L, H, device=v.device, dtype=v.dtype)
     db, dc, dv = (torch.empty(B, L, cols, device=v.device, dtype=v.dtype) for _ in range(3))
     torch.ops.spear_btp.gated_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, int(k))
+    kv = b_logits.shape[2] // 16
+    if kv < H:  # heads share key/value heads: the gradient of a shared head is the sum over its group
+        db = db.view(B, L, kv, H // kv, 16).sum(dim=3).reshape(B, L, kv * 16)
+        dc = dc.view(B, L, kv, H // kv, 16).sum(dim=3).reshape(B, L, kv * 16)
     return da, db, dc, dv
 
 
@@ -179,12 +198,14 @@ def gated_btp_wide(wide: torch.Tensor, heads: int, k: int = 2) -> torch.Tensor:
 def gated_btp(a_logits: torch.Tensor, b_logits: torch.Tensor, c: torch.Tensor, v: torch.Tensor, k: int = 2) -> torch.Tensor:
     """out[B, L, H*16] = btp(sigmoid(a_logits), sigmoid(b_logits) * v) * c + v, token-major throughout.
 
-    a_logits: [B, L, H]; b_logits, c, v: [B, L, H*16]; all CUDA bfloat16 with dense rows (they may be column
-    slices of one wider projection output).  H must be a multiple of 4 and L a multiple of 16.
+    a_logits: [B, L, H]; v: [B, L, H*16]; b_logits, c: [B, L, kv_heads*16] with kv_heads a divisor of H (kv_heads = H
+    when every head has its own; otherwise head h uses key/value head h // (H / kv_heads) and the shared columns
+    are read in place).  All CUDA bfloat16 with dense rows (they may be column slices of one wider projection
+    output).  H must be a multiple of 4 and L a multiple of 16.
     """
     if a_logits.dim() != 3:
         raise ValueError("a_logits must be [B, L, H]")
     H = a_logits.shape[2]
-    if not gated_btp_supported(H, H, a_logits.shape[1]):
+    if not gated_btp_supported(H, _kv_heads(b_logits, c, H), a_logits.shape[1]):
         raise ValueError(f"gated_btp needs heads % 4 == 0 and L % 16 == 0 (got H={H}, L={a_logits.shape[1]})")
     return _GatedBTP.apply(a_logits, b_logits, c, v, k)

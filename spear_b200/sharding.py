@@ -26,6 +26,35 @@ def batch_shard(global_batch: int, rank: int, world: int) -> tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
+def bind_to_gpu_numa_node(device_index: int) -> list[int]:
+    """Restricts the calling process to the CPU cores next to GPU `device_index` (NVML's ideal CPU affinity).
+
+    With several ranks on one box, pinned host buffers should live on the memory of the socket their GPU hangs
+    off: pages are placed where the thread that first touches them runs, and a copy whose host pages sit on the
+    other socket crosses the inter-socket link in addition to PCIe.  Call it before allocating and filling the
+    pinned buffers.  Only the CPU affinity of this process is changed (a per-process setting); nothing is written
+    to the GPU or the driver.  Returns the cores chosen, or [] when NVML or the affinity call is unavailable -
+    the process then stays where it is.
+    """
+    import os
+
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cores = [64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1]
+        allowed = sorted(set(cores) & os.sched_getaffinity(0))
+        if not allowed:
+            return []
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:
+        return []
+
+
 def _world(group=None) -> int:
     return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 

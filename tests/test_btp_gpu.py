@@ -663,6 +663,46 @@ def test_gated_backward_vs_oracle(native, B, L, H):
             assert err <= 1.5e-2, f"{name} k={k}: rel_l2 {err:.3e}"
 
 
+@pytest.mark.parametrize("B,L,H,kv", [(2, 64, 8, 4), (3, 208, 8, 2), (2, 96, 12, 4), (2, 1024, 16, 1), (40, 128, 16, 8)])
+def test_gated_kernels_read_shared_key_value_heads_in_place(native, B, L, H, kv):
+    """Heads that share key/value heads (KVRepeat, spear/nn/phalanx/swr.py:96-103: head h uses key/value head
+    h // (H / kv)): B_logits and C come as [B, L, kv*16] and go to the kernels as they are.  Forward and all four
+    gradients against the float32 oracle fed the REPEATED tensors (autograd then sums dB, dC over each group);
+    groups of 2, 3, 4, 16 and 2, one launch each way, nothing in between but the reduction over the group."""
+    from spear_b200 import _lib
+    from spear_b200.ops.btp.gated import gated_btp
+
+    g = torch.Generator().manual_seed(300 + L + kv)
+    cols, kcols, group = H * 16, kv * 16, H // kv
+    al = torch.randn(B, L, H, generator=g).bfloat16()
+    bl, c = (torch.randn(B, L, kcols, generator=g).bfloat16() for _ in range(2))
+    v = torch.randn(B, L, cols, generator=g).bfloat16()
+    dout = torch.randn(B, L, cols, generator=g).bfloat16()
+    rep = lambda t: t.reshape(B, L, kv, 1, 16).expand(B, L, kv, group, 16).reshape(B, L, cols)
+    for k in (2, 1):
+        ins = [t.cuda().requires_grad_(True) for t in (al, bl, c, v)]
+        n0 = _lib.launch_count()
+        out = gated_btp(*ins, k)
+        out.backward(dout.cuda())
+        assert _lib.launch_count() - n0 == 2  # one forward, one backward launch: no repeat copies in between
+        ref = [t.float().requires_grad_(True) for t in (al, bl, c, v)]
+        sig = torch.sigmoid(ref[0])
+        a = (sig + (sig.detach().bfloat16().float() - sig.detach())).transpose(1, 2)
+        heads = lambda t: t.reshape(B, L, H, 16).permute(0, 2, 3, 1)
+        x = torch.sigmoid(heads(rep(ref[1]))) * heads(ref[3])
+        y = O.btp_forward(a.contiguous(), x.contiguous(), k)
+        want = (y * heads(rep(ref[2])) + heads(ref[3])).permute(0, 3, 1, 2).reshape(B, L, cols)
+        want.backward(dout.float())
+        assert out.shape == want.shape
+        err = O.rel_l2(out.detach().float().cpu(), want.detach())
+        assert err <= 1e-2, f"out k={k}: rel_l2 {err:.3e}"
+        for name, got, exp in zip(("dA_logits", "dB_logits", "dC", "dV"), ins, ref):
+            assert got.grad.shape == exp.grad.shape, name
+            assert torch.isfinite(got.grad.float()).all(), name
+            err = O.rel_l2(got.grad.float().cpu(), exp.grad)
+            assert err <= 1.5e-2, f"{name} k={k}: rel_l2 {err:.3e}"
+
+
 def test_fused_projection_matches_separate_projections(native):
     """One wide GEMM feeding the gated kernels through row pitches vs four projections: same layer results."""
     from spear_b200.nn.phalanx import Phalanx
@@ -684,13 +724,39 @@ def test_fused_projection_matches_separate_projections(native):
     assert O.rel_l2(res[True][1], res[False][1]) <= 2e-2
     for name in res[True][2]:
         assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
+    # The four weights live as row slices of one packed matrix: a training step (an in-place update of the
+    # parameters) is seen by the next forward without any concatenation, and a forward launches no copy kernel.
+    from torch.profiler import ProfilerActivity, profile
+
+    layer.fused_projection = True
+    packed = layer._packed
+    assert packed is not None and packed.intact(layer.param)
+    opt = torch.optim.SGD(layer.parameters(), lr=0.05)
+    opt.step()
+    assert layer._packed is packed and packed.intact(layer.param)
+    ub = u.bfloat16()
+    with torch.no_grad():
+        stepped = layer(ub)
+        layer.fused_projection = False
+        assert O.rel_l2(stepped.float().cpu(), layer(ub).float().cpu()) <= 1e-2  # same (updated) weights on both paths
+        layer.fused_projection = True
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            layer(ub)
+            torch.cuda.synchronize()
+    names = [e.key for e in prof.key_averages() if e.device_type == torch.autograd.DeviceType.CUDA]
+    assert any("btp_gated_forward_kernel" in n for n in names), names
+    copies = [n for n in names if any(w in n.lower() for w in ("copy", "catarray", "fill"))]
+    assert not copies, f"copy kernels in a fused forward: {copies}"
+    assert layer._packed is packed
 
 
 @pytest.mark.parametrize("kv_heads", [8, 2])
 def test_shared_key_value_heads_run_fused(native, kv_heads):
-    """kv_heads < heads: the layer repeats B_logits and C to all heads and stays on the gated kernels.  Checked
-    against the float32 oracle of the reference's data flow (head h reads key/value head h // group) and against
-    the operation-by-operation path, gradients included."""
+    """kv_heads < heads: the layer hands the narrow B_logits and C to the gated kernels, which read the shared
+    columns in place.  Checked against the float32 oracle of the reference's data flow (head h reads key/value
+    head h // group) and against the operation-by-operation path, gradients included; with the torch profiler,
+    that no repeat / expand copy of a [B, L, dim] tensor runs between the projections and the gated kernel."""
     from spear_b200 import _lib
     from spear_b200.nn.phalanx import Phalanx
 
@@ -714,6 +780,22 @@ def test_shared_key_value_heads_run_fused(native, kv_heads):
     assert O.rel_l2(res[True][1], res[False][1]) <= 2e-2
     for name in res[True][2]:
         assert O.rel_l2(res[True][2][name], res[False][2][name]) <= 2e-2, name
+    # kernels of one fused forward: the projections' GEMMs, the cast of the input and the gated kernel - no
+    # elementwise or copy kernel that touches a full [B, L, dim] bf16 tensor for the repeat
+    from torch.profiler import ProfilerActivity, profile
+
+    layer.fused_gating = True
+    ui = u.cuda().bfloat16()  # already in the compute type: the layer's own cast is a no-op
+    with torch.no_grad():
+        layer(ui)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            layer(ui)
+            torch.cuda.synchronize()
+    names = [e.key for e in prof.key_averages() if e.device_type == torch.autograd.DeviceType.CUDA]
+    assert any("btp_gated_forward_kernel" in n for n in names), names
+    copies = [n for n in names if any(w in n.lower() for w in ("copy", "catarray", "index_select", "gather"))]
+    assert not copies, f"copy kernels between the projections and the gated kernel: {copies}"
 
 
 def test_concurrent_calls_from_several_threads(native):

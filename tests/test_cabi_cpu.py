@@ -40,7 +40,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_status_strings(lib):
-    assert lib.btp_sm100_abi_version() == 2
+    assert lib.btp_sm100_abi_version() == 3
     seen = set()
     for code in range(0, -10, -1):
         name = lib.btp_sm100_status_string(code).decode()
@@ -86,11 +86,16 @@ def test_argument_errors_come_back_as_codes(lib):
 def test_gated_entry_points_check_their_arguments(lib):
     p, ll = ctypes.c_void_p, ctypes.c_longlong
 
-    def fwd(B=1, L=16, H=4, k=2, ld=(4, 64, 64, 64, 64), ptrs=(16, 16, 16, 16, 16)):
-        return lib.btp_sm100_gated_forward(*[p(x) for x in ptrs], B, L, H, *[ll(x) for x in ld], k, p(0))
+    def fwd(B=1, L=16, H=4, k=2, ld=(4, 64, 64, 64, 64), ptrs=(16, 16, 16, 16, 16), kv=None):
+        return lib.btp_sm100_gated_forward(*[p(x) for x in ptrs], B, L, H, H if kv is None else kv, *[ll(x) for x in ld], k, p(0))
 
-    def bwd(B=1, L=16, H=4, k=2, ld=(4, 64, 64, 64, 64, 4, 64, 64, 64), ptrs=(16,) * 9):
-        return lib.btp_sm100_gated_backward(*[p(x) for x in ptrs], B, L, H, *[ll(x) for x in ld], k, p(0))
+    def bwd(B=1, L=16, H=4, k=2, ld=(4, 64, 64, 64, 64, 4, 64, 64, 64), ptrs=(16,) * 9, kv=None):
+        return lib.btp_sm100_gated_backward(*[p(x) for x in ptrs], B, L, H, H if kv is None else kv, *[ll(x) for x in ld], k, p(0))
+
+    assert fwd(kv=3) == -2 and "kv_heads must divide" in lib.btp_sm100_last_error().decode()
+    assert fwd(kv=0) == -2 and bwd(kv=3) == -2
+    assert fwd(kv=2, ld=(4, 24, 32, 64, 64)) == -2   # shared heads: B_logits row narrower than kv_heads*16
+    assert bwd(kv=2, ld=(4, 32, 32, 64, 64, 4, 32, 64, 64)) == -2   # dB_logits stays per head: pitch >= H*16
 
     assert fwd(H=6) == -2 and "multiple of 4" in lib.btp_sm100_last_error().decode()
     assert fwd(L=24) == -2

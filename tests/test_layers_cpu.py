@@ -122,3 +122,40 @@ def test_phalanx_forward_needs_a_gpu():
     layer = Phalanx(dim=64, length=32, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         layer(torch.randn(1, 32, 64, dtype=torch.bfloat16))
+
+
+def test_packed_projections_keep_parameters_and_follow_in_place_updates():
+    """The one-GEMM projection path keeps the four weights as row slices of one matrix: same parameters, same
+    state_dict, packed buffer follows optimizer steps and load_state_dict, and is rebuilt after `.to()`."""
+    from spear_b200.nn.phalanx.swr import _PackedProjections, _WideProjection
+
+    torch.manual_seed(0)
+    layer = Phalanx(dim=128, dtype=torch.float64)
+    prm = layer.param
+    names_before = list(layer.state_dict())
+    before = {k: v.clone() for k, v in layer.state_dict().items()}
+    params_before = [id(p) for p in layer.parameters()]
+    pk = _PackedProjections(prm)
+    assert pk.intact(prm) and list(layer.state_dict()) == names_before
+    assert [id(p) for p in layer.parameters()] == params_before  # the same Parameter objects
+    assert all(torch.equal(v, before[k]) for k, v in layer.state_dict().items())
+    u = torch.randn(2, 16, 128, dtype=torch.float64, requires_grad=True)
+    args = (prm.proj_b.weight, prm.proj_c.weight, prm.proj_v.weight, prm.proj_a.weight, prm.proj_b.bias, prm.proj_c.bias, prm.proj_a.bias)
+    wide = _WideProjection.apply(u, pk.weight, pk.bias, pk.offsets, *args)
+    ref = torch.cat([prm.proj_b(u), prm.proj_c(u), prm.proj_v(u), prm.proj_a(u)], -1)
+    assert torch.allclose(wide, ref)
+    g = torch.randn_like(wide)
+    wide.backward(g)
+    got = {n: p.grad.clone() for n, p in prm.named_parameters()}
+    du = u.grad.clone()
+    for p in prm.parameters():
+        p.grad = None
+    u.grad = None
+    ref.backward(g)
+    assert all(torch.allclose(p.grad, got[n]) for n, p in prm.named_parameters()) and torch.allclose(u.grad, du)
+    torch.optim.SGD(layer.parameters(), lr=0.1).step()  # in place: the packed matrix moves with the parameters
+    assert pk.intact(prm) and torch.equal(pk.weight[:128], prm.proj_b.weight) and not torch.equal(pk.weight[:128], before["param.proj_b.weight"])
+    layer.load_state_dict(before)
+    assert pk.intact(prm) and torch.equal(pk.weight[:128], before["param.proj_b.weight"])
+    layer.to(torch.float32)  # fresh storage for every parameter: the link is gone and is noticed
+    assert not pk.intact(prm)

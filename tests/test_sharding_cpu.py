@@ -133,3 +133,28 @@ def test_sequence_sharding_with_halo_exchange(tmp_path, world):
     for rank in range(world):
         res = json.load(open(f"{out}.{rank}"))
         assert max(res.values()) < 1e-12, (rank, res)
+
+
+def test_bind_to_gpu_numa_node_uses_the_affinity_nvml_reports(monkeypatch):
+    """With a stand-in for NVML: the process ends up on the reported cores that it is allowed to use, and a
+    missing NVML leaves it where it is."""
+    import types
+
+    from spear_b200.sharding import bind_to_gpu_numa_node
+
+    before = os.sched_getaffinity(0)
+    first = min(before)
+    fake = types.ModuleType("pynvml")
+    fake.nvmlInit = lambda: None
+    fake.nvmlDeviceGetHandleByIndex = lambda i: i
+    fake.nvmlDeviceGetCpuAffinity = lambda h, words: [(1 << (first % 64)) if w == first // 64 else 0 for w in range(words)]
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    try:
+        assert bind_to_gpu_numa_node(0) == [first]
+        assert os.sched_getaffinity(0) == {first}
+    finally:
+        os.sched_setaffinity(0, before)
+    fake.nvmlDeviceGetCpuAffinity = lambda h, words: [0] * words  # no usable core reported: nothing changes
+    assert bind_to_gpu_numa_node(0) == [] and os.sched_getaffinity(0) == before
+    monkeypatch.setitem(sys.modules, "pynvml", None)  # import fails
+    assert bind_to_gpu_numa_node(0) == [] and os.sched_getaffinity(0) == before
