@@ -454,6 +454,14 @@ def main():
             torch.cuda.empty_cache()
             return r
 
+        # what a launch of the forward kernel's size can reach at all: a plain device copy of x-sized tensors
+        # (read 2 B, write 2 B per element) in the same kind of loop
+        cs = [(torch.randn(1024, 32, D, 128, device=dev, generator=gen).bfloat16(),
+               torch.empty(1024, 32, D, 128, device=dev, dtype=torch.bfloat16)) for _ in range(3)]
+        copy_us = over_ranks_max([statistics.median(loop_us(lambda i: cs[i % 3][1].copy_(cs[i % 3][0]), nk, 3))])[0]
+        copy_bytes = 2 * cs[0][0].numel() * 2
+        del cs
+        torch.cuda.empty_cache()
         # configs[3]: long sequences, near-unit decays given as float32 log a (4 more bytes per head-token)
         f3, b3, s3 = over_ranks_max(plain_pair(16, 64, 8192, "f32log", True))
         # the BTP part of configs[4] (Phalanx layer, dim 2048, L 2048, global batch 64) in the plain layout
@@ -472,6 +480,10 @@ def main():
                     "fwd_bwd_gbs": (fb_ + bb_) * ht_ / s_us / 1e3,
                     "tokens_per_s_per_gpu": nb * length / (s_us * 1e-6)}
 
+        extra["same_size_copy"] = {
+            "what": "torch copy_ of a [1024,32,16,128] bf16 tensor (268 MB read + written), the practical ceiling for a launch "
+                    "of the forward kernel's size; the roofline peak is the rate of a 4 GiB copy",
+            "us_per_launch": copy_us, "gbs": copy_bytes / copy_us / 1e3}
         extra["configs3"] = cfg_line("btp fwd+bwd B=16 H=64 L=8192 per GPU, float32 log a ~ U(-1e-3,0), bf16 x/dy",
                                      16, 64, 8192, FWD_BYTES_PER_HT + 2, BWD_BYTES_PER_HT + 2, f3, b3, s3)
         extra["configs4_btp_part"] = cfg_line("btp fwd+bwd B=64 H=128 L=2048 per GPU, bf16 (plain layout)",

@@ -48,17 +48,22 @@ extern "C" {
 #define BTP_ERR_DEVICE_TIMEOUT (-8) /* a bounded wait inside a kernel gave up (btp_sm100_device_status) */
 #define BTP_ERR_TOO_LARGE (-9)      /* problem exceeds the built-in scratch of btp_sm100_forward_noalloc */
 
-/* dtype tags */
+/* dtype tags.  x and dx are 16-bit: bfloat16 unless the call says float16 (the reference takes both,
+ * csrc/btp/_bindings.cu:29-31).  A call says float16 activations through its coefficient tag: BTP_DTYPE_F16 (a
+ * float16 coefficient), or BTP_DTYPE_F32 / BTP_DTYPE_F32_LOG or'ed with BTP_ACT_F16.  y and dy are float32 or the
+ * activations' own 16-bit type. */
 #define BTP_DTYPE_BF16 0        /* x, y, dy, dx, coeff */
 #define BTP_DTYPE_F32 1         /* y, dy;  coeff given in linear space as float */
 #define BTP_DTYPE_F32_LOG 2     /* coeff only: natural log of the coefficient, float (superset of the reference) */
+#define BTP_DTYPE_F16 3         /* x, y, dy, dx, coeff as float16 */
+#define BTP_ACT_F16 0x10        /* flag on a float coefficient tag: the activations are float16 */
 
 /*
  * Forward:  y = btp(coeff, x).
  * Replaces spear._btp.forward (csrc/btp/_bindings.cu:76-150 -> btp-forward.cu:85-457).
- *   coeff        [B,H,L]      coeff_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F32 | BTP_DTYPE_F32_LOG
- *   x            [B,H,16,L]   bf16
- *   y            [B,H,16,L]   out_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F32
+ *   coeff        [B,H,L]      coeff_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F16 | BTP_DTYPE_F32 | BTP_DTYPE_F32_LOG (see the tags)
+ *   x            [B,H,16,L]   bf16 (float16 when the coefficient tag says so)
+ *   y            [B,H,16,L]   out_dtype: x's type | BTP_DTYPE_F32
  *   checkpoint   [B,H,L/16,16] float, or NULL.  When given and k == 2, slot j < L/16-1 receives the
  *                block-local last token of block j, exactly the tensor the reference's forward
  *                saves (btp-forward.cu:369-373).  The backward below does not need it.
@@ -70,10 +75,10 @@ int btp_sm100_forward(const void* coeff, const void* x, void* y, float* checkpoi
 /*
  * Backward:  (dx, dA) for upstream gradient dy.
  * Replaces spear._btp.backward (csrc/btp/_bindings.cu:152-229 -> btp-backwards.cu:165-808).
- *   dy           [B,H,16,L]   dy_dtype: BTP_DTYPE_BF16 | BTP_DTYPE_F32
+ *   dy           [B,H,16,L]   dy_dtype: x's type | BTP_DTYPE_F32
  *   checkpoint   accepted for signature compatibility and ignored (may be NULL): the carry is
  *                recomputed from x and coeff, which costs no extra memory traffic.
- *   dx           [B,H,16,L]   bf16
+ *   dx           [B,H,16,L]   x's type
  *   dA           [B,H,L]      float, gradient w.r.t. the linear coefficient (w.r.t. the log
  *                coefficient when coeff_dtype == BTP_DTYPE_F32_LOG)
  */

@@ -18,6 +18,8 @@ LIB_PATH = os.path.join(_HERE, "lib", "libbtp_sm100.so")
 DTYPE_BF16 = 0
 DTYPE_F32 = 1
 DTYPE_F32_LOG = 2
+DTYPE_F16 = 3
+ACT_F16 = 0x10  # flag on a float coefficient tag: the activations are float16
 
 ABI_VERSION = 3
 

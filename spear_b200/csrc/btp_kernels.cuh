@@ -37,7 +37,7 @@
 
 namespace btp {
 
-constexpr int kCoefBf16 = 0;    // linear coefficient, bf16
+constexpr int kCoefBf16 = 0;    // linear coefficient in the activations' 16-bit type (bf16, or fp16 for the fp16 kernels)
 constexpr int kCoefF32 = 1;     // linear coefficient, float
 constexpr int kCoefF32Log = 2;  // natural-log coefficient, float
 
@@ -340,17 +340,17 @@ __device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], flo
 }
 
 // Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables at `tab`.
-template <int COEF, int TL, bool BWD>
+template <int COEF, int TL, bool BWD, bool F16 = false>
 __device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane, float carry_scale) {
   constexpr int TPL = TL / 32;  // tokens per lane: 2 or 4
   float v[TPL];
   if constexpr (COEF == kCoefBf16) {
     if constexpr (TPL == 4) {
       const uint2 raw = reinterpret_cast<const uint2*>(rawp)[lane];
-      v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
+      v[0] = Act<F16>::lo(raw.x); v[1] = Act<F16>::hi(raw.x); v[2] = Act<F16>::lo(raw.y); v[3] = Act<F16>::hi(raw.y);
     } else {
       const uint32_t raw = reinterpret_cast<const uint32_t*>(rawp)[lane];
-      v[0] = bf16_lo(raw); v[1] = bf16_hi(raw);
+      v[0] = Act<F16>::lo(raw); v[1] = Act<F16>::hi(raw);
     }
   } else {
     if constexpr (TPL == 4) {
@@ -374,13 +374,13 @@ __device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int l
 // w() represents a weight exactly like the Lmat operand of the tensor-core path: one bf16 term, or two
 // (hi + lo) when PRECISE.
 // Returns the values for channels g and g+8 (g = lane >> 2), identical in the 4 lanes of a group.
-template <int COEF, bool TILE_F32, bool RIGHT, bool PRECISE>
+template <int COEF, bool TILE_F32, bool RIGHT, bool PRECISE, bool F16 = false>
 __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* coeff_base, int L, long long bh,
                                             int tok0, int lane, float& out_g, float& out_g8) {
   const int g = lane >> 2, t = lane & 3;
   float a;
   if constexpr (COEF == kCoefBf16) {
-    a = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(coeff_base)[bh * L + tok0 + (lane & 15)]);
+    a = Act<F16>::scalar(reinterpret_cast<const unsigned short*>(coeff_base)[bh * L + tok0 + (lane & 15)]);
   } else {
     a = reinterpret_cast<const float*>(coeff_base)[bh * L + tok0 + (lane & 15)];
   }
@@ -396,7 +396,7 @@ __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* c
   for (int j = 0; j < 4; ++j) {
     const int tok = 2 * t + (j & 1) + ((j >> 1) << 3);
     const float Tj = __shfl_sync(0xffffffffu, T, tok);
-    w[j] = lmat_weight<PRECISE>(ex2(RIGHT ? (Tj - Tref) : (Tref - Tj)));
+    w[j] = act_weight<F16, PRECISE>(ex2(RIGHT ? (Tj - Tref) : (Tref - Tj)));
   }
   float e[2][4];  // [row half][token]
   const long long row_g = (bh * 16 + g) * static_cast<long long>(L) + tok0;
@@ -408,18 +408,18 @@ __device__ __forceinline__ void halo_reduce(const void* tile_base, const void* c
     const float2 b0 = *reinterpret_cast<const float2*>(p + row_g8 + 2 * t);
     const float2 b1 = *reinterpret_cast<const float2*>(p + row_g8 + 8 + 2 * t);
     // what the tensor-core path feeds: dy as one bf16 term, or as two (hi + lo) when PRECISE
-    e[0][0] = lmat_weight<PRECISE>(a0.x); e[0][1] = lmat_weight<PRECISE>(a0.y);
-    e[0][2] = lmat_weight<PRECISE>(a1.x); e[0][3] = lmat_weight<PRECISE>(a1.y);
-    e[1][0] = lmat_weight<PRECISE>(b0.x); e[1][1] = lmat_weight<PRECISE>(b0.y);
-    e[1][2] = lmat_weight<PRECISE>(b1.x); e[1][3] = lmat_weight<PRECISE>(b1.y);
+    e[0][0] = act_weight<F16, PRECISE>(a0.x); e[0][1] = act_weight<F16, PRECISE>(a0.y);
+    e[0][2] = act_weight<F16, PRECISE>(a1.x); e[0][3] = act_weight<F16, PRECISE>(a1.y);
+    e[1][0] = act_weight<F16, PRECISE>(b0.x); e[1][1] = act_weight<F16, PRECISE>(b0.y);
+    e[1][2] = act_weight<F16, PRECISE>(b1.x); e[1][3] = act_weight<F16, PRECISE>(b1.y);
   } else {
-    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(tile_base);
+    const unsigned short* p = reinterpret_cast<const unsigned short*>(tile_base);
     const uint32_t a0 = *reinterpret_cast<const uint32_t*>(p + row_g + 2 * t);
     const uint32_t a1 = *reinterpret_cast<const uint32_t*>(p + row_g + 8 + 2 * t);
     const uint32_t b0 = *reinterpret_cast<const uint32_t*>(p + row_g8 + 2 * t);
     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(p + row_g8 + 8 + 2 * t);
-    e[0][0] = bf16_lo(a0); e[0][1] = bf16_hi(a0); e[0][2] = bf16_lo(a1); e[0][3] = bf16_hi(a1);
-    e[1][0] = bf16_lo(b0); e[1][1] = bf16_hi(b0); e[1][2] = bf16_lo(b1); e[1][3] = bf16_hi(b1);
+    e[0][0] = Act<F16>::lo(a0); e[0][1] = Act<F16>::hi(a0); e[0][2] = Act<F16>::lo(a1); e[0][3] = Act<F16>::hi(a1);
+    e[1][0] = Act<F16>::lo(b0); e[1][1] = Act<F16>::hi(b0); e[1][2] = Act<F16>::lo(b1); e[1][3] = Act<F16>::hi(b1);
   }
   float sg = 0.0f, sg8 = 0.0f;
 #pragma unroll
@@ -475,6 +475,7 @@ struct LmatFrag {
 };
 
 // tg = &T[g], tt = &T[2t] of the chunk; `off` = 16 * block index (a compile-time constant in the hot loops)
+template <bool F16 = false>
 __device__ __forceinline__ LmatFrag build_lmat(const float* tg, const float* tt, int off, const TileLane& tl) {
   const float Tg = tg[off];
   const float Tg8 = tg[off + 8];
@@ -487,17 +488,19 @@ __device__ __forceinline__ LmatFrag build_lmat(const float* tg, const float* tt,
   const float e4 = tl.m0 ? ex2(Tg8 - Tb.x) : 0.0f;
   const float e5 = tl.m1 ? ex2(Tg8 - Tb.y) : 0.0f;
   LmatFrag f;
-  f.b00 = pack_bf16x2(e0, e1);
-  f.b10 = pack_bf16x2(e2, e3);
-  f.b11 = pack_bf16x2(e4, e5);
+  f.b00 = Act<F16>::pack(e0, e1);
+  f.b10 = Act<F16>::pack(e2, e3);
+  f.b11 = Act<F16>::pack(e4, e5);
   return f;
 }
 
 // code 1: a bounded wait gave up; code 2: shared-memory base not 1024-byte aligned
 // The same fragments split into two bf16 terms, Lmat = hi + lo with |lo| <= 2^-9 |hi|: feeding both to the
 // tensor cores reproduces the fp32 Lmat to about 2^-17 instead of 2^-9.
+template <bool F16 = false>
 __device__ __forceinline__ void build_lmat_split(const float* tg, const float* tt, int off, const TileLane& tl,
                                                  LmatFrag& hi, LmatFrag& lo) {
+  using A = Act<F16>;
   const float Tg = tg[off];
   const float Tg8 = tg[off + 8];
   const float2 Ta = *reinterpret_cast<const float2*>(tt + off);
@@ -508,12 +511,12 @@ __device__ __forceinline__ void build_lmat_split(const float* tg, const float* t
   const float e3 = ex2(Tg8 - Ta.y);
   const float e4 = tl.m0 ? ex2(Tg8 - Tb.x) : 0.0f;
   const float e5 = tl.m1 ? ex2(Tg8 - Tb.y) : 0.0f;
-  hi.b00 = pack_bf16x2(e0, e1);
-  hi.b10 = pack_bf16x2(e2, e3);
-  hi.b11 = pack_bf16x2(e4, e5);
-  lo.b00 = pack_bf16x2(e0 - bf16_lo(hi.b00), e1 - bf16_hi(hi.b00));
-  lo.b10 = pack_bf16x2(e2 - bf16_lo(hi.b10), e3 - bf16_hi(hi.b10));
-  lo.b11 = pack_bf16x2(e4 - bf16_lo(hi.b11), e5 - bf16_hi(hi.b11));
+  hi.b00 = A::pack(e0, e1);
+  hi.b10 = A::pack(e2, e3);
+  hi.b11 = A::pack(e4, e5);
+  lo.b00 = A::pack(e0 - A::lo(hi.b00), e1 - A::hi(hi.b00));
+  lo.b10 = A::pack(e2 - A::lo(hi.b10), e3 - A::hi(hi.b10));
+  lo.b11 = A::pack(e4 - A::lo(hi.b11), e5 - A::hi(hi.b11));
 }
 
 __device__ __forceinline__ void report_error(unsigned int code, int warp, int chunk) {
@@ -528,7 +531,8 @@ __device__ __forceinline__ void report_error(unsigned int code, int warp, int ch
 // Forward
 // =====================================================================================
 // PRECISE: Lmat goes to the tensor cores as two bf16 terms (see build_lmat_split).
-template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
+// F16: activations (x, y, a 16-bit coefficient) are float16 instead of bfloat16.
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16 = false>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const __grid_constant__ CUtensorMap tm_c, const KernelParams p) {
@@ -612,12 +616,12 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int nt = chunk_tiles<TL, RAGGED>(cons.cs, L);
     const int c0 = cons.cs * TL;
     float* tab = ws.tab_ptr(0);
-    chunk_tables<COEF, TL, false>(ws.raw_ptr(s), tab, lane, carry_scale);
+    chunk_tables<COEF, TL, false, F16>(ws.raw_ptr(s), tab, lane, carry_scale);
 
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
     } else if (cons.fresh) {  // the block to the left belongs to another warp (or another run)
-      halo_reduce<COEF, false, false, PRECISE>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
+      halo_reduce<COEF, false, false, PRECISE, F16>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
     }
 
     const float* tg = tab + tl.g;
@@ -640,18 +644,18 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const int box = i >> 2, ib = i & 3;
         LmatFrag lf, lo;
         if constexpr (PRECISE) {
-          build_lmat_split(tg, tt, 16 * i, tl, lf, lo);
+          build_lmat_split<F16>(tg, tt, 16 * i, tl, lf, lo);
         } else {
-          lf = build_lmat(tg, tt, 16 * i, tl);
+          lf = build_lmat<F16>(tg, tt, 16 * i, tl);
         }
         uint32_t a0, a1, a2, a3;
         ldmatrix_x4(ldm + box * 2048 + tl.ldm_off[ib], a0, a1, a2, a3);
         float v0[4], v1[4];
-        mma_1688(v0, a0, a1, lf.b00);
-        mma_16816(v1, a0, a1, a2, a3, lf.b10, lf.b11);
+        Act<F16>::mma8(v0, a0, a1, lf.b00);
+        Act<F16>::mma16(v1, a0, a1, a2, a3, lf.b10, lf.b11);
         if constexpr (PRECISE) {
-          mma_1688_acc(v0, a0, a1, lo.b00);
-          mma_16816_acc(v1, a0, a1, a2, a3, lo.b10, lo.b11);
+          Act<F16>::mma8_acc(v0, a0, a1, lo.b00);
+          Act<F16>::mma16_acc(v1, a0, a1, a2, a3, lo.b10, lo.b11);
         }
         const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
         const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);
@@ -686,10 +690,10 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           // shared-memory instructions of a warp execute in program order.
           const uint32_t o0 = stb + box * 2048 + tl.st_off[ib];
           const uint32_t o1 = o0 ^ 16u;
-          st_shared_u32(o0, pack_bf16x2(y0[0], y0[1]));
-          st_shared_u32(o0 + 1024, pack_bf16x2(y0[2], y0[3]));
-          st_shared_u32(o1, pack_bf16x2(y1[0], y1[1]));
-          st_shared_u32(o1 + 1024, pack_bf16x2(y1[2], y1[3]));
+          st_shared_u32(o0, Act<F16>::pack(y0[0], y0[1]));
+          st_shared_u32(o0 + 1024, Act<F16>::pack(y0[2], y0[3]));
+          st_shared_u32(o1, Act<F16>::pack(y1[0], y1[1]));
+          st_shared_u32(o1 + 1024, Act<F16>::pack(y1[2], y1[3]));
         }
       }
     }
@@ -732,7 +736,7 @@ struct TileAcc {
 
 // PRECISE: the Lmat operand goes to the tensor cores as two bf16 terms (4 more products per block), which
 // brings dA to the accuracy of a float32 evaluation; without it Lmat is rounded to bf16 once.
-template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16 = false>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                     const __grid_constant__ CUtensorMap tm_dx, const __grid_constant__ CUtensorMap tm_c,
@@ -816,9 +820,9 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const int box = i >> 2, ib = i & 3;
     LmatFrag lf, lo;
     if constexpr (PRECISE) {
-      build_lmat_split(tg, tt, 16 * i, tl, lf, lo);
+      build_lmat_split<F16>(tg, tt, 16 * i, tl, lf, lo);
     } else {
-      lf = build_lmat(tg, tt, 16 * i, tl);
+      lf = build_lmat<F16>(tg, tt, 16 * i, tl);
     }
     // dy . Lmat needs the transposed 8x8 blocks as B operand (k = r, n = c)
     const uint32_t g00 = movmatrix_trans(lf.b00);
@@ -840,8 +844,8 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       // A float32 dy goes to the tensor cores as two bf16 terms as well (hi + lo), so that dA keeps float32
       // accuracy for float32 upstream gradients (the op's default output type makes them float32).
       auto split = [&](const float2 f, uint32_t& hi, uint32_t& lo) {
-        hi = pack_bf16x2(f.x, f.y);
-        if constexpr (PRECISE) lo = pack_bf16x2(f.x - bf16_lo(hi), f.y - bf16_hi(hi));
+        hi = Act<F16>::pack(f.x, f.y);
+        if constexpr (PRECISE) lo = Act<F16>::pack(f.x - Act<F16>::lo(hi), f.y - Act<F16>::hi(hi));
       };
       split(lds(bb + ((c_lo ^ tl.g) << 4) + in), e0, l0);
       split(lds(bb + 1024 + ((c_lo ^ tl.g) << 4) + in), e1, l1);
@@ -850,18 +854,19 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     } else {
       ldmatrix_x4(dy_s + tl.ldm_base + box * 2048 + tl.ldm_off[ib], e0, e1, e2, e3);
     }
-    mma_1688(acc.v0, a0, a1, lf.b00);
-    mma_16816(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
-    mma_16816(acc.g0, e0, e1, e2, e3, g00, g10);
-    mma_1688(acc.g1, e2, e3, g11);
+    using A = Act<F16>;
+    A::mma8(acc.v0, a0, a1, lf.b00);
+    A::mma16(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
+    A::mma16(acc.g0, e0, e1, e2, e3, g00, g10);
+    A::mma8(acc.g1, e2, e3, g11);
     if constexpr (PRECISE) {
-      mma_1688_acc(acc.v0, a0, a1, lo.b00);
-      mma_16816_acc(acc.v1, a0, a1, a2, a3, lo.b10, lo.b11);
-      mma_16816_acc(acc.g0, e0, e1, e2, e3, movmatrix_trans(lo.b00), movmatrix_trans(lo.b10));
-      mma_1688_acc(acc.g1, e2, e3, movmatrix_trans(lo.b11));
+      A::mma8_acc(acc.v0, a0, a1, lo.b00);
+      A::mma16_acc(acc.v1, a0, a1, a2, a3, lo.b10, lo.b11);
+      A::mma16_acc(acc.g0, e0, e1, e2, e3, movmatrix_trans(lo.b00), movmatrix_trans(lo.b10));
+      A::mma8_acc(acc.g1, e2, e3, movmatrix_trans(lo.b11));
       if constexpr (DY_F32) {  // dy_lo . Lmat_hi (the lo . lo term is below float32 resolution)
-        mma_16816_acc(acc.g0, l0, l1, l2, l3, g00, g10);
-        mma_1688_acc(acc.g1, l2, l3, g11);
+        A::mma16_acc(acc.g0, l0, l1, l2, l3, g00, g10);
+        A::mma8_acc(acc.g1, l2, l3, g11);
       }
     }
     // gradient this block sends to its left neighbour: P[0] * gw[:,0]   (P[0] = Pshift[1])
@@ -925,10 +930,10 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     }
     // dx replaces the consumed x block in shared memory
     const uint32_t o1 = o0 ^ 16u;
-    st_shared_u32(o0, pack_bf16x2(dx0[0], dx0[1]));
-    st_shared_u32(o0 + 1024, pack_bf16x2(dx0[2], dx0[3]));
-    st_shared_u32(o1, pack_bf16x2(dx1[0], dx1[1]));
-    st_shared_u32(o1 + 1024, pack_bf16x2(dx1[2], dx1[3]));
+    st_shared_u32(o0, Act<F16>::pack(dx0[0], dx0[1]));
+    st_shared_u32(o0 + 1024, Act<F16>::pack(dx0[2], dx0[3]));
+    st_shared_u32(o1, Act<F16>::pack(dx1[0], dx1[1]));
+    st_shared_u32(o1 + 1024, Act<F16>::pack(dx1[2], dx1[3]));
   };
 
   // pending block = last block of the previous chunk; its accumulators live in slot B
@@ -970,9 +975,9 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const int nt = chunk_tiles<TL, RAGGED>(cons.cs, L);
     const int c0 = cons.cs * TL;
     float* tab = ws.tab_ptr(tset);
-    chunk_tables<COEF, TL, true>(ws.raw_ptr(s), tab, lane, carry_scale);
+    chunk_tables<COEF, TL, true, F16>(ws.raw_ptr(s), tab, lane, carry_scale);
     if (j == 0 && cons.cs != 0 && p.use_carry) {
-      halo_reduce<COEF, false, false, PRECISE>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
+      halo_reduce<COEF, false, false, PRECISE, F16>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
     }
     const float* tg = tab + tl.g;
     const float* tt = tab + 2 * tl.t;
@@ -1032,7 +1037,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     float dc_g = 0.0f, dc_g8 = 0.0f;
     if (!p_seq_end && p.use_carry) {
       // the block to the right belongs to another warp: recompute what it sends
-      halo_reduce<COEF, DY_F32, true, PRECISE>(p.dy, p.coeff, L, p_bh, p_c0 + 16 * p_nt, lane, dc_g, dc_g8);
+      halo_reduce<COEF, DY_F32, true, PRECISE, F16>(p.dy, p.coeff, L, p_bh, p_c0 + 16 * p_nt, lane, dc_g, dc_g8);
     }
     back(accB, p_tt, p_da, p_o0, p_cg, p_cg8, dc_g, dc_g8);
     flush();

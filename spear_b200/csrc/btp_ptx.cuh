@@ -243,6 +243,79 @@ __device__ __forceinline__ float lmat_weight(float v) {
   }
 }
 
+// ---------------------------------------------------------------- the 16-bit activation type: bfloat16 or float16
+// The kernels are written once; Act<F16> supplies what differs between the two 16-bit types - packing and
+// unpacking of pairs, and the tensor-core instruction (the reference takes both, csrc/btp/_bindings.cu:29-31).
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float f16_bits_to_float(unsigned short h) {
+  float f;
+  asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h));
+  return f;
+}
+__device__ __forceinline__ void mma_16816_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ void mma_1688_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0), "f"(0.0f));
+}
+__device__ __forceinline__ void mma_16816_acc_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_1688_acc_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0));
+}
+
+template <bool F16>
+struct Act {  // bfloat16
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) { return pack_bf16x2(lo, hi); }
+  static __device__ __forceinline__ float lo(uint32_t v) { return bf16_lo(v); }
+  static __device__ __forceinline__ float hi(uint32_t v) { return bf16_hi(v); }
+  static __device__ __forceinline__ float scalar(unsigned short h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
+  static __device__ __forceinline__ void mma16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) { mma_16816(d, a0, a1, a2, a3, b0, b1); }
+  static __device__ __forceinline__ void mma8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) { mma_1688(d, a0, a1, b0); }
+  static __device__ __forceinline__ void mma16_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) { mma_16816_acc(d, a0, a1, a2, a3, b0, b1); }
+  static __device__ __forceinline__ void mma8_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) { mma_1688_acc(d, a0, a1, b0); }
+};
+template <>
+struct Act<true> {  // float16
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) { return pack_f16x2(lo, hi); }
+  static __device__ __forceinline__ float lo(uint32_t v) { return f16_bits_to_float(static_cast<unsigned short>(v & 0xffffu)); }
+  static __device__ __forceinline__ float hi(uint32_t v) { return f16_bits_to_float(static_cast<unsigned short>(v >> 16)); }
+  static __device__ __forceinline__ float scalar(unsigned short h) { return f16_bits_to_float(h); }
+  static __device__ __forceinline__ void mma16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) { mma_16816_f16(d, a0, a1, a2, a3, b0, b1); }
+  static __device__ __forceinline__ void mma8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) { mma_1688_f16(d, a0, a1, b0); }
+  static __device__ __forceinline__ void mma16_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t b0, uint32_t b1) { mma_16816_acc_f16(d, a0, a1, a2, a3, b0, b1); }
+  static __device__ __forceinline__ void mma8_acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) { mma_1688_acc_f16(d, a0, a1, b0); }
+};
+// Value that the tensor-core path effectively multiplies by when `v` is fed as one 16-bit term or as two (hi + lo).
+template <bool F16, bool SPLIT>
+__device__ __forceinline__ float act_weight(float v) {
+  const float hi = Act<F16>::lo(Act<F16>::pack(v, 0.0f));
+  if constexpr (SPLIT) {
+    return hi + Act<F16>::lo(Act<F16>::pack(v - hi, 0.0f));
+  } else {
+    return hi;
+  }
+}
+
 __device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }

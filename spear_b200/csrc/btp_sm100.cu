@@ -238,12 +238,10 @@ struct Dims {
   int total_chunks;
 };
 
-int check_common(const char* fn, int B, int H, int L, int k, int coeff_dtype, Dims* d) {
+int check_common(const char* fn, int B, int H, int L, int k, Dims* d) {
   if (B <= 0 || H <= 0 || L <= 0) return fail(BTP_ERR_BAD_SHAPE, "%s: B, H, L must be positive (got %d, %d, %d)", fn, B, H, L);
   if (L % 16 != 0) return fail(BTP_ERR_BAD_SHAPE, "%s: L must be a multiple of 16 (got %d)", fn, L);
   if (k != 1 && k != 2) return fail(BTP_ERR_BAD_ORDER, "%s: k must be 1 or 2 (got %d)", fn, k);
-  if (coeff_dtype != BTP_DTYPE_BF16 && coeff_dtype != BTP_DTYPE_F32 && coeff_dtype != BTP_DTYPE_F32_LOG)
-    return fail(BTP_ERR_BAD_DTYPE, "%s: unsupported coefficient dtype tag %d", fn, coeff_dtype);
   d->B = B; d->H = H; d->L = L;
   d->BH = static_cast<long long>(B) * H;
   if (d->BH * 16 > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: B*H*16 = %lld rows exceeds the 2^31-1 limit", fn, d->BH * 16);
@@ -279,10 +277,10 @@ int forward_run_len(const Dims& d, long long nwarps) {
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 // ------------------------------------------------------------------ forward dispatch
-template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16>
 int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
-  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, RAGGED, PRECISE, NBOX, STAGES, WARPS>;
+  auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, RAGGED, PRECISE, NBOX, STAGES, WARPS, F16>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
   DeviceInfo info;
@@ -313,35 +311,66 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
 }
 
 // Sequences that are a whole number of chunks get the kernel without ragged-chunk handling.
-template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool OUT_F32, bool CKPT, int NBOX, int STAGES, int WARPS, bool F16>
 int launch_forward(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
   const bool ragged = d.L % (64 * NBOX) != 0;
-  if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
-  return launch_forward_impl<COEF, OUT_F32, CKPT, true, true, NBOX, STAGES, WARPS>(coeff, x, y, ckpt, d, k, stream);
+  if (!ragged) return launch_forward_impl<COEF, OUT_F32, CKPT, false, true, NBOX, STAGES, WARPS, F16>(coeff, x, y, ckpt, d, k, stream);
+  return launch_forward_impl<COEF, OUT_F32, CKPT, true, true, NBOX, STAGES, WARPS, F16>(coeff, x, y, ckpt, d, k, stream);
 }
 
 // Launch shape of the forward kernel: 128-token chunks (2 boxes), 3 stages, 4 warps per CTA (16 warps per SM).
-template <int COEF, bool OUT_F32, bool CKPT>
+template <int COEF, bool OUT_F32, bool CKPT, bool F16>
 int forward_variant(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t s) {
-  return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 4>(coeff, x, y, ckpt, d, k, s);
+  return launch_forward<COEF, OUT_F32, CKPT, 2, 3, 4, F16>(coeff, x, y, ckpt, d, k, s);
 }
 
-template <int COEF>
+template <int COEF, bool F16>
 int forward_coef(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, int out_dtype, cudaStream_t s) {
   const bool f32 = out_dtype == BTP_DTYPE_F32;
   const bool ck = ckpt != nullptr && k == 2;
-  if (f32) return ck ? forward_variant<COEF, true, true>(coeff, x, y, ckpt, d, k, s)
-                     : forward_variant<COEF, true, false>(coeff, x, y, ckpt, d, k, s);
-  return ck ? forward_variant<COEF, false, true>(coeff, x, y, ckpt, d, k, s)
-            : forward_variant<COEF, false, false>(coeff, x, y, ckpt, d, k, s);
+  if (f32) return ck ? forward_variant<COEF, true, true, F16>(coeff, x, y, ckpt, d, k, s)
+                     : forward_variant<COEF, true, false, F16>(coeff, x, y, ckpt, d, k, s);
+  return ck ? forward_variant<COEF, false, true, F16>(coeff, x, y, ckpt, d, k, s)
+            : forward_variant<COEF, false, false, F16>(coeff, x, y, ckpt, d, k, s);
+}
+
+// Decodes the dtype tags of a call: which 16-bit type the activations have, the coefficient's form, and whether
+// the 16-bit output / upstream-gradient tag agrees with the activations.
+struct Types {
+  bool f16;    // activations (x, dx, a 16-bit y / dy / coefficient) are float16, else bfloat16
+  int coef;    // kCoefBf16 (16-bit, in the activation type), kCoefF32, kCoefF32Log
+};
+int decode_types(const char* fn, int coeff_dtype, int io_dtype, const char* io_name, Types* t) {
+  const int kind = coeff_dtype & 0xf;
+  const bool flag = (coeff_dtype & BTP_ACT_F16) != 0;
+  if ((coeff_dtype & ~(0xf | BTP_ACT_F16)) != 0 || kind > BTP_DTYPE_F16)
+    return fail(BTP_ERR_BAD_DTYPE, "%s: unsupported coefficient dtype tag %d", fn, coeff_dtype);
+  if (kind == BTP_DTYPE_BF16 && flag)
+    return fail(BTP_ERR_BAD_DTYPE, "%s: a bfloat16 coefficient cannot go with float16 activations", fn);
+  t->f16 = flag || kind == BTP_DTYPE_F16;
+  t->coef = kind == BTP_DTYPE_F32 ? kCoefF32 : (kind == BTP_DTYPE_F32_LOG ? kCoefF32Log : kCoefBf16);
+  const int same = t->f16 ? BTP_DTYPE_F16 : BTP_DTYPE_BF16;
+  if (io_dtype != BTP_DTYPE_F32 && io_dtype != same)
+    return fail(BTP_ERR_BAD_DTYPE, "%s: %s must be float32 or the activations' own 16-bit type (tag %d, got %d)", fn, io_name,
+                same, io_dtype);
+  return BTP_OK;
+}
+
+template <bool F16>
+int forward_types(int coef, const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, int out_dtype, cudaStream_t s) {
+  switch (coef) {
+    case kCoefBf16: return forward_coef<kCoefBf16, F16>(coeff, x, y, ckpt, d, k, out_dtype, s);
+    case kCoefF32: return forward_coef<kCoefF32, F16>(coeff, x, y, ckpt, d, k, out_dtype, s);
+    default: return forward_coef<kCoefF32Log, F16>(coeff, x, y, ckpt, d, k, out_dtype, s);
+  }
 }
 
 // ------------------------------------------------------------------ backward dispatch
-template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool DY_F32, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16>
 int launch_backward_impl(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
                          cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, true, DY_F32>;
-  auto kern = btp_backward_kernel<COEF, DY_F32, RAGGED, PRECISE, NBOX, STAGES, WARPS>;
+  auto kern = btp_backward_kernel<COEF, DY_F32, RAGGED, PRECISE, NBOX, STAGES, WARPS, F16>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
   DeviceInfo info;
@@ -368,18 +397,34 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
   return BTP_OK;
 }
 
-template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS>
+template <int COEF, bool DY_F32, int NBOX, int STAGES, int WARPS, bool F16>
 int launch_backward(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
                     cudaStream_t stream) {
   const bool ragged = d.L % (64 * NBOX) != 0;
-  if (!ragged) return launch_backward_impl<COEF, DY_F32, false, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
-  return launch_backward_impl<COEF, DY_F32, true, true, NBOX, STAGES, WARPS>(coeff, x, dy, dx, dA, d, k, stream);
+  if (!ragged) return launch_backward_impl<COEF, DY_F32, false, true, NBOX, STAGES, WARPS, F16>(coeff, x, dy, dx, dA, d, k, stream);
+  return launch_backward_impl<COEF, DY_F32, true, true, NBOX, STAGES, WARPS, F16>(coeff, x, dy, dx, dA, d, k, stream);
 }
 
 // Launch shape of the backward kernel: 64-token chunks, 3 x-stages + 2 dy-stages, 4 warps per CTA.
-template <int COEF, bool DY_F32>
+template <int COEF, bool DY_F32, bool F16>
 int backward_variant(const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k, cudaStream_t s) {
-  return launch_backward<COEF, DY_F32, 1, 3, 4>(coeff, x, dy, dx, dA, d, k, s);
+  return launch_backward<COEF, DY_F32, 1, 3, 4, F16>(coeff, x, dy, dx, dA, d, k, s);
+}
+
+template <bool F16>
+int backward_types(int coef, bool f32, const void* coeff, const void* x, const void* dy, void* dx, float* dA, Dims d, int k,
+                   cudaStream_t s) {
+  switch (coef) {
+    case kCoefBf16:
+      return f32 ? backward_variant<kCoefBf16, true, F16>(coeff, x, dy, dx, dA, d, k, s)
+                 : backward_variant<kCoefBf16, false, F16>(coeff, x, dy, dx, dA, d, k, s);
+    case kCoefF32:
+      return f32 ? backward_variant<kCoefF32, true, F16>(coeff, x, dy, dx, dA, d, k, s)
+                 : backward_variant<kCoefF32, false, F16>(coeff, x, dy, dx, dA, d, k, s);
+    default:
+      return f32 ? backward_variant<kCoefF32Log, true, F16>(coeff, x, dy, dx, dA, d, k, s)
+                 : backward_variant<kCoefF32Log, false, F16>(coeff, x, dy, dx, dA, d, k, s);
+  }
 }
 
 // ------------------------------------------------------------------ gated forward launch
@@ -532,55 +577,43 @@ extern "C" {
 int btp_sm100_forward(const void* coeff, const void* x, void* y, float* checkpoint, int B, int H, int L, int k,
                       int coeff_dtype, int out_dtype, void* stream) {
   Dims d{};
-  int rc = check_common("btp_sm100_forward", B, H, L, k, coeff_dtype, &d);
+  int rc = check_common("btp_sm100_forward", B, H, L, k, &d);
   if (rc) return rc;
-  if (out_dtype != BTP_DTYPE_BF16 && out_dtype != BTP_DTYPE_F32)
-    return fail(BTP_ERR_BAD_DTYPE, "btp_sm100_forward: unsupported output dtype tag %d", out_dtype);
+  Types t{};
+  if ((rc = decode_types("btp_sm100_forward", coeff_dtype, out_dtype, "y", &t))) return rc;
   if (!coeff || !x || !y) return fail(BTP_ERR_NULL_POINTER, "btp_sm100_forward: coeff, x and y must not be NULL");
   if (misaligned(coeff) || misaligned(x) || misaligned(y) || misaligned(checkpoint))
     return fail(BTP_ERR_MISALIGNED, "btp_sm100_forward: every pointer must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (coeff_dtype) {
-    case BTP_DTYPE_BF16: return forward_coef<kCoefBf16>(coeff, x, y, checkpoint, d, k, out_dtype, s);
-    case BTP_DTYPE_F32: return forward_coef<kCoefF32>(coeff, x, y, checkpoint, d, k, out_dtype, s);
-    default: return forward_coef<kCoefF32Log>(coeff, x, y, checkpoint, d, k, out_dtype, s);
-  }
+  return t.f16 ? forward_types<true>(t.coef, coeff, x, y, checkpoint, d, k, out_dtype, s)
+               : forward_types<false>(t.coef, coeff, x, y, checkpoint, d, k, out_dtype, s);
 }
 
 int btp_sm100_backward(const void* coeff, const void* x, const void* dy, const float* checkpoint, void* dx, float* dA,
                        int B, int H, int L, int k, int coeff_dtype, int dy_dtype, void* stream) {
   (void)checkpoint;  // the carry is recomputed; see the header
   Dims d{};
-  int rc = check_common("btp_sm100_backward", B, H, L, k, coeff_dtype, &d);
+  int rc = check_common("btp_sm100_backward", B, H, L, k, &d);
   if (rc) return rc;
-  if (dy_dtype != BTP_DTYPE_BF16 && dy_dtype != BTP_DTYPE_F32)
-    return fail(BTP_ERR_BAD_DTYPE, "btp_sm100_backward: unsupported dy dtype tag %d", dy_dtype);
+  Types t{};
+  if ((rc = decode_types("btp_sm100_backward", coeff_dtype, dy_dtype, "dy", &t))) return rc;
   if (!coeff || !x || !dy || !dx || !dA)
     return fail(BTP_ERR_NULL_POINTER, "btp_sm100_backward: coeff, x, dy, dx and dA must not be NULL");
   if (misaligned(coeff) || misaligned(x) || misaligned(dy) || misaligned(dx) || misaligned(dA))
     return fail(BTP_ERR_MISALIGNED, "btp_sm100_backward: every pointer must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool f32 = dy_dtype == BTP_DTYPE_F32;
-  switch (coeff_dtype) {
-    case BTP_DTYPE_BF16:
-      return f32 ? backward_variant<kCoefBf16, true>(coeff, x, dy, dx, dA, d, k, s)
-                 : backward_variant<kCoefBf16, false>(coeff, x, dy, dx, dA, d, k, s);
-    case BTP_DTYPE_F32:
-      return f32 ? backward_variant<kCoefF32, true>(coeff, x, dy, dx, dA, d, k, s)
-                 : backward_variant<kCoefF32, false>(coeff, x, dy, dx, dA, d, k, s);
-    default:
-      return f32 ? backward_variant<kCoefF32Log, true>(coeff, x, dy, dx, dA, d, k, s)
-                 : backward_variant<kCoefF32Log, false>(coeff, x, dy, dx, dA, d, k, s);
-  }
+  return t.f16 ? backward_types<true>(t.coef, f32, coeff, x, dy, dx, dA, d, k, s)
+               : backward_types<false>(t.coef, f32, coeff, x, dy, dx, dA, d, k, s);
 }
 
 int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, int H, int L, int k, int coeff_dtype,
                               int out_dtype, void* stream) {
   Dims d{};
-  int rc = check_common("btp_sm100_forward_noalloc", B, H, L, k, coeff_dtype, &d);
+  int rc = check_common("btp_sm100_forward_noalloc", B, H, L, k, &d);
   if (rc) return rc;
-  if (out_dtype != BTP_DTYPE_BF16 && out_dtype != BTP_DTYPE_F32)
-    return fail(BTP_ERR_BAD_DTYPE, "btp_sm100_forward_noalloc: unsupported output dtype tag %d", out_dtype);
+  Types t{};
+  if ((rc = decode_types("btp_sm100_forward_noalloc", coeff_dtype, out_dtype, "y", &t))) return rc;
   if (!coeff || !x || !y) return fail(BTP_ERR_NULL_POINTER, "btp_sm100_forward_noalloc: coeff, x and y must not be NULL");
   if (misaligned(coeff) || misaligned(x) || misaligned(y))
     return fail(BTP_ERR_MISALIGNED, "btp_sm100_forward_noalloc: every pointer must be 16-byte aligned");
@@ -598,11 +631,8 @@ int btp_sm100_forward_noalloc(const void* coeff, const void* x, void* y, int B, 
   float* scratch = nullptr;
   if (k == 2 && (rc = noalloc_scratch(&scratch))) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (coeff_dtype) {
-    case BTP_DTYPE_BF16: return forward_coef<kCoefBf16>(coeff, x, y, scratch, d, k, out_dtype, s);
-    case BTP_DTYPE_F32: return forward_coef<kCoefF32>(coeff, x, y, scratch, d, k, out_dtype, s);
-    default: return forward_coef<kCoefF32Log>(coeff, x, y, scratch, d, k, out_dtype, s);
-  }
+  return t.f16 ? forward_types<true>(t.coef, coeff, x, y, scratch, d, k, out_dtype, s)
+               : forward_types<false>(t.coef, coeff, x, y, scratch, d, k, out_dtype, s);
 }
 
 int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const void* c, const void* v, void* out, int B,

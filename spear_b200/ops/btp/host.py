@@ -20,13 +20,13 @@ __all__ = ["btp_fwd_bwd_host"]
 class _Ring:
     """Device buffers for `depth` slices in flight."""
 
-    def __init__(self, depth, nb, H, L, coeff_dtype, dy_dtype, y_dtype, device):
+    def __init__(self, depth, nb, H, L, x_dtype, coeff_dtype, dy_dtype, y_dtype, device):
         mk = lambda shape, dt: [torch.empty(shape, device=device, dtype=dt) for _ in range(depth)]
         self.a = mk((nb, H, L), coeff_dtype)
-        self.x = mk((nb, H, 16, L), torch.bfloat16)
+        self.x = mk((nb, H, 16, L), x_dtype)
         self.dy = mk((nb, H, 16, L), dy_dtype)
         self.y = mk((nb, H, 16, L), y_dtype)
-        self.dx = mk((nb, H, 16, L), torch.bfloat16)
+        self.dx = mk((nb, H, 16, L), x_dtype)
         self.dA = mk((nb, H, L), torch.float32)
         self.free = [torch.cuda.Event() for _ in range(depth)]  # slice buffers fully downloaded
 
@@ -38,8 +38,8 @@ _rings: dict = {}
 def btp_fwd_bwd_host(coeff, x, dy, y, dx, dA, *, k: int = 2, slices: int = 8, depth: int = 3, device=None):
     """y = btp(coeff, x); (dx, dA) = its gradients for upstream dy - all six tensors in pinned host memory.
 
-    coeff [B,H,L] (bf16 or fp32), x, dy [B,H,16,L] (x bf16; dy bf16 or fp32) are read; y (bf16 or fp32),
-    dx (bf16), dA (fp32) are written.  The batch is processed in `slices` pieces with `depth` of them in
+    coeff [B,H,L] (x's 16-bit type or fp32), x, dy [B,H,16,L] (x bf16 or fp16; dy x's type or fp32) are read;
+    y (x's type or fp32), dx (x's type), dA (fp32) are written.  The batch is processed in `slices` pieces with `depth` of them in
     flight.  Returns after enqueueing; synchronise the device (or the current stream) before reading the outputs.
     """
     if any(t.is_cuda for t in (coeff, x, dy, y, dx, dA)):
@@ -50,11 +50,11 @@ def btp_fwd_bwd_host(coeff, x, dy, y, dx, dA, *, k: int = 2, slices: int = 8, de
     B, H, D, L = x.shape
     slices = max(1, min(slices, B))
     nb = (B + slices - 1) // slices
-    key = (device.index, depth, nb, H, L, coeff.dtype, dy.dtype, y.dtype)
+    key = (device.index, depth, nb, H, L, x.dtype, coeff.dtype, dy.dtype, y.dtype)
     ring = _rings.get(key)
     if ring is None:
         _rings.clear()  # one shape at a time: do not hoard device memory
-        ring = _rings[key] = _Ring(depth, nb, H, L, coeff.dtype, dy.dtype, y.dtype, device)
+        ring = _rings[key] = _Ring(depth, nb, H, L, x.dtype, coeff.dtype, dy.dtype, y.dtype, device)
         ring.streams = (torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device))
     s_in, s_run, s_out = ring.streams
     caller = torch.cuda.current_stream(device)

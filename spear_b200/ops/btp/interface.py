@@ -12,7 +12,7 @@ Differences, all deliberate:
 * ``dA`` is not pre-zeroed: the kernel writes every element.
 * ``coeff`` may also be float32, and with ``coeff_space="log"`` it is the natural
   log of the coefficient (float32) - a superset for decays that bf16 cannot hold.
-* bf16 activations only; there is no CPU path and no fallback.
+* bfloat16 or float16 activations (as in the reference); there is no CPU path and no fallback.
 """
 
 from __future__ import annotations
@@ -138,8 +138,8 @@ def btp(
     """Block two-pass sliding-window recurrence (signature of interface.py:164-188).
 
     Args:
-        coeff: [B, H, L] decay coefficients in (0, 1]; bfloat16 (as in the reference) or float32.
-        x: [B, H, 16, L] bfloat16 driving term.
+        coeff: [B, H, L] decay coefficients in (0, 1]; x's 16-bit type (as in the reference) or float32.
+        x: [B, H, 16, L] bfloat16 or float16 driving term.
         k: 2 = local pass plus one-hop carry, 1 = local pass only.
         wpb: accepted for compatibility ({4, 8, 16, 32}); the kernels choose their own launch shape.
         output_dtype: dtype of the result, default float32 (as in the reference).

@@ -407,6 +407,68 @@ def test_long_sequences_with_near_unit_float32_decays_at_full_size(native, log_c
     assert rel <= 5e-6, f"dA rel_l2 against float64 {rel:.3e}"
 
 
+@pytest.mark.parametrize("B,H,L,k,coeff_kind,f32_io", [(2, 4, 512, 2, 0, False), (3, 5, 208, 2, 1, True), (1, 2, 4096, 2, 2, False),
+                                                       (4, 8, 128, 1, 0, True), (64, 32, 128, 2, 0, False), (2, 3, 1040, 2, 1, False)])
+def test_float16_activations_vs_oracle(native, B, H, L, k, coeff_kind, f32_io):
+    """The reference takes float16 as well as bfloat16 (csrc/btp/_bindings.cu:29-31): x, a 16-bit coefficient, and
+    y / dy / dx in float16.  Same oracle, same bounds; the inputs are float16-representable, so the oracle sees
+    exactly what the kernel is given.  float16 has three more mantissa bits than bfloat16, so the outputs are
+    closer to the oracle (the error is the rounding of the 16-bit output)."""
+    g = torch.Generator().manual_seed(1600 + L + coeff_kind)
+    x = (torch.randn(B, H, 16, L, generator=g)).half()
+    dy = torch.randn(B, H, 16, L, generator=g).half()
+    a32 = torch.sigmoid(torch.randn(B, H, L, generator=g) * 1.5)
+    if coeff_kind == 0:
+        a, coeff, cdt = a32.half().float(), a32.half(), torch.float16
+    elif coeff_kind == 1:
+        a, coeff, cdt = a32, a32, torch.float32
+    else:
+        a, coeff, cdt = a32, torch.log(a32), torch.float32
+    io = torch.float32 if f32_io else torch.float16
+    y_w = O.btp_forward(a.double(), x.double(), k)
+    dA_w, dx_w = O.btp_backward(a.double(), x.double(), dy.double(), k)
+    if coeff_kind == 2:
+        dA_w = dA_w * a.double()
+    xd, cd, dyd = x.cuda(), coeff.to(cdt).cuda(), dy.to(io).cuda()
+    y = torch.full((B, H, 16, L), float("nan"), device="cuda", dtype=io)
+    dx = torch.full((B, H, 16, L), float("nan"), device="cuda", dtype=torch.float16)
+    dA = torch.full((B, H, L), float("nan"), device="cuda")
+    native.forward(cd, xd, y, None, k, 32, log_coeff=coeff_kind == 2)
+    native.backward(cd, xd, dyd, None, dx, dA, k, 32, log_coeff=coeff_kind == 2)
+    torch.cuda.synchronize()
+    assert_limits(y.float().cpu(), y_w.float(), FORWARD_LIMITS, "y")
+    assert_limits(dx.float().cpu(), dx_w.float(), BACKWARD_LIMITS, "dx")
+    assert_limits(dA.cpu(), dA_w.float(), BACKWARD_LIMITS, "dA")
+    assert O.rel_l2(y.double().cpu(), y_w) <= (1e-5 if f32_io else 4e-4)   # float32 y: the two-term Lmat; float16 y: its rounding
+    assert O.rel_l2(dx.double().cpu(), dx_w) <= 4e-4
+    assert O.rel_l2(dA.double().cpu(), dA_w) <= 5e-6
+    # bfloat16 and float16 must not be mixed
+    with pytest.raises(RuntimeError):
+        native.forward(cd if cdt == torch.float32 else cd.bfloat16(), xd, torch.empty_like(xd, dtype=torch.bfloat16), None, k, 32)
+    with pytest.raises(RuntimeError):
+        native.forward(a32.bfloat16().cuda(), xd, y, None, k, 32)
+
+
+def test_float16_through_the_public_wrapper(native):
+    """btp() with float16 inputs: default float32 output, autograd gradients in the inputs' types."""
+    from spear_b200.ops.btp import btp
+
+    g = torch.Generator().manual_seed(1616)
+    B, H, L = 2, 4, 256
+    x = torch.randn(B, H, 16, L, generator=g).half()
+    a = torch.sigmoid(torch.randn(B, H, L, generator=g)).half()
+    dy = torch.randn(B, H, 16, L, generator=g)
+    ad, xd = a.cuda().requires_grad_(True), x.cuda().requires_grad_(True)
+    y = btp(ad, xd)
+    assert y.dtype == torch.float32
+    y.backward(dy.cuda())
+    dA_w, dx_w = O.btp_backward(a.double(), x.double(), dy.double())
+    assert xd.grad.dtype == torch.float16 and ad.grad.dtype == torch.float16
+    assert O.rel_l2(y.detach().double().cpu(), O.btp_forward(a.double(), x.double())) <= 1e-5
+    assert O.rel_l2(xd.grad.double().cpu(), dx_w) <= 1e-3
+    assert O.rel_l2(ad.grad.double().cpu(), dA_w) <= 1e-3
+
+
 # ------------------------------------------------------------------ argument checking at the boundary
 def test_bad_arguments_raise(native):
     x = torch.zeros(1, 2, 16, 32, device="cuda", dtype=torch.bfloat16)

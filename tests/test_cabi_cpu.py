@@ -83,6 +83,27 @@ def test_argument_errors_come_back_as_codes(lib):
     assert _bwd(lib, dx=24) == -5
 
 
+def test_dtype_tags_of_the_plain_entry_points(lib):
+    """bfloat16 or float16 activations, chosen through the coefficient tag; y / dy float32 or the activations' type."""
+    p = ctypes.c_void_p
+
+    def fwd(ctag, otag):
+        return lib.btp_sm100_forward(p(16), p(16), p(16), p(0), 1, 1, 16, 2, ctag, otag, p(0))
+
+    def bwd(ctag, dtag):
+        return lib.btp_sm100_backward(p(16), p(16), p(16), p(0), p(16), p(16), 1, 1, 16, 2, ctag, dtag, p(0))
+
+    BF16, F32, LOG, F16, ACT = 0, 1, 2, 3, 0x10
+    for call in (fwd, bwd):
+        assert call(BF16 | ACT, F32) == -4 and "bfloat16 coefficient cannot go with float16" in lib.btp_sm100_last_error().decode()
+        assert call(4, F32) == -4 and call(0x20, F32) == -4          # unknown tag, unknown flag
+        assert call(BF16, F16) == -4 and call(F16, BF16) == -4        # 16-bit y / dy of the other type
+        assert call(F32 | ACT, BF16) == -4 and call(LOG, F16) == -4
+        # valid combinations get past the dtype checks (and fail later only for want of a GPU, or succeed)
+        for ctag, otag in ((BF16, BF16), (BF16, F32), (F32, BF16), (LOG, F32), (F16, F16), (F16, F32), (F32 | ACT, F16), (LOG | ACT, F32)):
+            assert call(ctag, otag) != -4, (ctag, otag)
+
+
 def test_gated_entry_points_check_their_arguments(lib):
     p, ll = ctypes.c_void_p, ctypes.c_longlong
 
