@@ -268,9 +268,8 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
         LmatFrag lf, lo;
         build_lmat_split(tg, tt, 16 * i, tl, lf, lo);
         float v0[4], v1[4];
-        mma_1688(v0, x0, x1, lf.b00);
+        mma_16816(v0, x0, x1, x0, x1, lf.b00, lo.b00);  // hi and lo term of the 8-token product in one k = 16 instruction
         mma_16816(v1, x0, x1, x2, x3, lf.b10, lf.b11);
-        mma_1688_acc(v0, x0, x1, lo.b00);
         mma_16816_acc(v1, x0, x1, x2, x3, lo.b10, lo.b11);
         const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
         const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);

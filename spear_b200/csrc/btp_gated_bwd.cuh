@@ -221,14 +221,13 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
     const float* tt = tab + 2 * tl.t;
     LmatFrag lf, lo;
     build_lmat_split(tg, tt, 16 * i, tl, lf, lo);
-    mma_1688(pd.v0, x[0], x[1], lf.b00);
+    // the two 8-token products take their hi and lo terms in one k = 16 instruction each (left operand given twice)
+    mma_16816(pd.v0, x[0], x[1], x[0], x[1], lf.b00, lo.b00);
     mma_16816(pd.v1, x[0], x[1], x[2], x[3], lf.b10, lf.b11);
-    mma_1688_acc(pd.v0, x[0], x[1], lo.b00);
     mma_16816_acc(pd.v1, x[0], x[1], x[2], x[3], lo.b10, lo.b11);
     mma_16816(pd.g0, dy[0], dy[1], dy[2], dy[3], movmatrix_trans(lf.b00), movmatrix_trans(lf.b10));
-    mma_1688(pd.g1, dy[2], dy[3], movmatrix_trans(lf.b11));
     mma_16816_acc(pd.g0, dy[0], dy[1], dy[2], dy[3], movmatrix_trans(lo.b00), movmatrix_trans(lo.b10));
-    mma_1688_acc(pd.g1, dy[2], dy[3], movmatrix_trans(lo.b11));
+    mma_16816(pd.g1, dy[2], dy[3], dy[2], dy[3], movmatrix_trans(lf.b11), movmatrix_trans(lo.b11));
     // y = v + P * carry;  dC = dOut * y
     const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
     const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);

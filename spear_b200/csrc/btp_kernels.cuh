@@ -651,11 +651,14 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         uint32_t a0, a1, a2, a3;
         ldmatrix_x4(ldm + box * 2048 + tl.ldm_off[ib], a0, a1, a2, a3);
         float v0[4], v1[4];
-        Act<F16>::mma8(v0, a0, a1, lf.b00);
-        Act<F16>::mma16(v1, a0, a1, a2, a3, lf.b10, lf.b11);
         if constexpr (PRECISE) {
-          Act<F16>::mma8_acc(v0, a0, a1, lo.b00);
+          // first eight tokens: x0 . hi + x0 . lo as ONE k = 16 product, the operand x0 given twice
+          Act<F16>::mma16(v0, a0, a1, a0, a1, lf.b00, lo.b00);
+          Act<F16>::mma16(v1, a0, a1, a2, a3, lf.b10, lf.b11);
           Act<F16>::mma16_acc(v1, a0, a1, a2, a3, lo.b10, lo.b11);
+        } else {
+          Act<F16>::mma8(v0, a0, a1, lf.b00);
+          Act<F16>::mma16(v1, a0, a1, a2, a3, lf.b10, lf.b11);
         }
         const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
         const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);
@@ -855,19 +858,24 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
       ldmatrix_x4(dy_s + tl.ldm_base + box * 2048 + tl.ldm_off[ib], e0, e1, e2, e3);
     }
     using A = Act<F16>;
-    A::mma8(acc.v0, a0, a1, lf.b00);
-    A::mma16(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
-    A::mma16(acc.g0, e0, e1, e2, e3, g00, g10);
-    A::mma8(acc.g1, e2, e3, g11);
     if constexpr (PRECISE) {
-      A::mma8_acc(acc.v0, a0, a1, lo.b00);
+      // The two 8-token products (x0 . L00 and dy1 . L11) take their hi and lo terms in ONE k = 16 instruction
+      // each, with the left operand given twice; the two 16-token products take two instructions.
+      A::mma16(acc.v0, a0, a1, a0, a1, lf.b00, lo.b00);
+      A::mma16(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
       A::mma16_acc(acc.v1, a0, a1, a2, a3, lo.b10, lo.b11);
+      A::mma16(acc.g0, e0, e1, e2, e3, g00, g10);
       A::mma16_acc(acc.g0, e0, e1, e2, e3, movmatrix_trans(lo.b00), movmatrix_trans(lo.b10));
-      A::mma8_acc(acc.g1, e2, e3, movmatrix_trans(lo.b11));
+      A::mma16(acc.g1, e2, e3, e2, e3, g11, movmatrix_trans(lo.b11));
       if constexpr (DY_F32) {  // dy_lo . Lmat_hi (the lo . lo term is below float32 resolution)
         A::mma16_acc(acc.g0, l0, l1, l2, l3, g00, g10);
         A::mma8_acc(acc.g1, l2, l3, g11);
       }
+    } else {
+      A::mma8(acc.v0, a0, a1, lf.b00);
+      A::mma16(acc.v1, a0, a1, a2, a3, lf.b10, lf.b11);
+      A::mma16(acc.g0, e0, e1, e2, e3, g00, g10);
+      A::mma8(acc.g1, e2, e3, g11);
     }
     // gradient this block sends to its left neighbour: P[0] * gw[:,0]   (P[0] = Pshift[1])
     const float a_first = tab[TL + 16 * i + 1];
