@@ -51,9 +51,9 @@ BWD_BYTES_PER_HT = 102   # coeff 2 + x 32 + dy 32 + dx 32 + dA 4
 NOMINAL_HBM_GBS = 8000.0  # the peak BASELINE.json's north star names
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from an ncu capture of
-# this command with one input set: 276.9 MB read + 117.5 MB written (the remaining 33.5 MB of the 151 MB of
+# this command with one input set: 276.9 MB read + 114.0 MB written (the remaining 37 MB of the 151 MB of
 # output were still in L2 when the single profiled launch ended).
-BWD_TRAFFIC_BYTES = 394_406_144
+BWD_TRAFFIC_BYTES = 390_901_504
 METRIC = "btp_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
