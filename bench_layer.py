@@ -44,15 +44,18 @@ def _timed(fn, steps, warm=3):
     return e0.elapsed_time(e1) / steps * 1e3  # us
 
 
-def bench_gated(B, L, H, steps, sets):
+def bench_gated(B, L, H, steps, sets, kv=None):
+    """kv: number of key/value heads (default H: every head its own); B_logits and C are [B, L, kv*16] then."""
     from spear_b200 import _lib
     from spear_b200.ops.btp import gated as G
 
     cols = H * 16
+    kv = H if kv is None else kv
     data = []
     for _ in range(sets):
         al = torch.randn(B, L, H, device="cuda").bfloat16()
-        bl, c, v, do = (torch.randn(B, L, cols, device="cuda").bfloat16() for _ in range(4))
+        bl, c = (torch.randn(B, L, kv * 16, device="cuda").bfloat16() for _ in range(2))
+        v, do = (torch.randn(B, L, cols, device="cuda").bfloat16() for _ in range(2))
         data.append((al, bl, c, v, do, torch.empty_like(v)))
     i = [0]
 
@@ -69,9 +72,15 @@ def bench_gated(B, L, H, steps, sets):
     ht = B * L * H
     tf, tb = _timed(fwd, steps), _timed(bwd, steps)
     _lib.device_status()
+    # algorithmic bytes per head-token: shared B_logits / C are read once per key/value head, and the kernel
+    # writes dB_logits / dC summed over the runs of heads it shares (see gated._shared_run)
+    run = G._shared_run(H, kv)
+    fwd_bytes = GATED_FWD_BYTES - 64 + 64 * kv / H
+    bwd_bytes = GATED_BWD_BYTES - 64 + 64 * kv / H - 64 + 64 / run
     return {
-        "what": "gated_btp", "B": B, "L": L, "H": H, "fwd_us": tf, "bwd_us": tb,
-        "fwd_gbs": GATED_FWD_BYTES * ht / tf / 1e3, "bwd_gbs": GATED_BWD_BYTES * ht / tb / 1e3,
+        "what": "gated_btp", "B": B, "L": L, "H": H, "kv_heads": kv, "fwd_us": tf, "bwd_us": tb,
+        "fwd_bytes_per_head_token": fwd_bytes, "bwd_bytes_per_head_token": bwd_bytes,
+        "fwd_gbs": fwd_bytes * ht / tf / 1e3, "bwd_gbs": bwd_bytes * ht / tb / 1e3,
         "fwd_bwd_tokens_per_s": B * L / ((tf + tb) * 1e-6),
     }
 
@@ -132,6 +141,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--sets", type=int, default=3)
     ap.add_argument("--what", default="both", choices=["gated", "layer", "both"])
+    ap.add_argument("--kv-heads", type=int, default=None, help="gated: key/value heads shared by groups of heads")
     ap.add_argument("--decay-mix", action="store_true", help="layer: fixed decays, half the heads near 1, half fast")
     ap.add_argument("--allreduce-grads", action="store_true", help="layer, several ranks: sum parameter gradients each step")
     args = ap.parse_args()
@@ -143,7 +153,7 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     try:
         if args.what in ("gated", "both") and rank == 0:
-            print(json.dumps(bench_gated(args.batch, args.length, args.dim // 16, args.steps, args.sets)), flush=True)
+            print(json.dumps(bench_gated(args.batch, args.length, args.dim // 16, args.steps, args.sets, args.kv_heads)), flush=True)
         if args.what in ("layer", "both"):
             res = bench_layer(args.batch, args.length, args.dim, max(3, args.steps // 10), decay_mix=args.decay_mix,
                               allreduce_grads=args.allreduce_grads, rank=rank, world=world)

@@ -150,9 +150,12 @@ int btp_sm100_gated_forward(const void* a_logits, const void* b_logits, const vo
  *   da_logits                 [B, L, H]    bf16  (pitch a multiple of 4 elements, base 8-byte aligned)
  *   db_logits, dc, dv         [B, L, H*16] bf16
  * Pitches (elements) follow the pointers in the same order; constraints as for the forward.
- * With kv_heads < H, b_logits and c are [B, L, kv_heads*16] (read in place, as in the forward) while db_logits
- * and dc are still written PER HEAD, [B, L, H*16]: the gradient of a shared key/value head is the sum of these
- * over the heads of its group, which is left to the caller (one reduction; autograd does the same for KVRepeat).
+ * With kv_heads < H, b_logits and c are [B, L, kv_heads*16] (read in place, as in the forward).  db_logits and
+ * dc are then [B, L, H*16 / r]: the kernel sums the gradients of runs of r neighbouring heads that share a
+ * key/value head - r = 4 when the group size H / kv_heads is a multiple of 4, r = 2 when it is 2, r = 1
+ * otherwise.  For groups of 2 and 4 that is the gradient of the key/value head itself, [B, L, kv_heads*16];
+ * for larger or odd groups the caller adds up the group / r partial sums per key/value head (columns
+ * [kv][group / r][16]; autograd does the whole sum for KVRepeat).
  */
 int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
                              void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, int kv_heads,

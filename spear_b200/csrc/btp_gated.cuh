@@ -19,7 +19,7 @@
 //
 // Shared key/value heads (SHARED == true; KVRepeat, swr.py:96-103: head h reads key/value head h / group).
 // B_logits and C are then [B, L, kv_heads*16] and are read IN PLACE: each warp fetches the 16 columns of its
-// key/value head as its own dense [tokens][16 channels] tile (32-byte rows, no swizzle), so the heads of a group
+// key/value head as its own dense [tokens][16 channels] tile (32-byte rows, 32-byte swizzle), so the heads of a group
 // fetch the same global columns - once from HBM, the repeats from L2 - and nothing is repeated in memory.
 #pragma once
 
@@ -214,8 +214,10 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
 
   // lane-constant addressing of this warp's [16 tokens][16 channels] block inside a box (see the header)
   const uint32_t frag_off = ((lane & 7) + 8 * (lane >> 4)) * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
-  // the same block inside this warp's dense [TL][16 channels] tile of a shared key/value head
-  const uint32_t kv_off = SHARED ? warp * (TL * 32) + ((lane & 7) + 8 * (lane >> 4)) * 32 + ((lane >> 3) & 1) * 16 : frag_off;
+  // the same block inside this warp's dense [TL][16 channels] tile of a shared key/value head (32-byte rows with
+  // the 32-byte swizzle: the two 16-byte halves of rows 4..7 of every 8 rows are exchanged, which spreads the
+  // eight rows of an 8x8 matrix over all banks)
+  const uint32_t kv_off = SHARED ? warp * (TL * 32) + ((lane & 7) + 8 * (lane >> 4)) * 32 + ((((lane >> 3) ^ (lane >> 2)) & 1) << 4) : frag_off;
   constexpr uint32_t kKvBlock = SHARED ? 512 : 2048;  // bytes from one 16-token block to the next
   float cg = 0.0f, cg8 = 0.0f;
   int s = 0;

@@ -14,9 +14,11 @@
 // the gradient that its right neighbour sends), so a block's operands and accumulators wait in registers.
 //
 // Shared key/value heads (SHARED == true): B_logits and C are [B, L, kv_heads*16] and are read in place, each
-// warp fetching its key/value head's 16 columns as a dense tile of its own (see btp_gated.cuh).  dB_logits and
-// dC are still produced PER HEAD, [B, L, H*16] (the tile a warp loaded is the tile it overwrites); the caller
-// sums them over the heads of a group, which is the one reduction autograd would do anyway.
+// warp fetching its key/value head's 16 columns as a dense tile of its own (see btp_gated.cuh).  Each warp
+// overwrites its tile with its head's dB_logits / dC; before they leave, the CTA sums the tiles of neighbouring
+// heads that share a key/value head: runs of r = 4 heads when the group size is a multiple of 4, of r = 2 when it
+// is 2, none otherwise.  The outputs are [B, L, H*16/r]: already the gradient of the key/value head when
+// r equals the group size, else partial sums that the caller adds up (group/r of them per key/value head).
 #pragma once
 
 #include "btp_gated.cuh"
@@ -92,7 +94,28 @@ struct GatedPending {
   uint32_t df[4];      // dOut
 };
 
-template <int STAGES, bool SHARED>
+// Sums the [TL][16] bf16 tiles of each run of R neighbouring heads into the run's first tile, in float32.  A tile is
+// TL*32 bytes = 128 units of 8 bytes = one unit per thread; a thread reads its unit from the R tiles of a run and
+// writes it back to the first of them, so no thread touches another thread's unit.
+template <int R>
+__device__ __forceinline__ void sum_head_tiles(unsigned char* slot, int tid) {
+  static_assert(kGbTL * 32 == 128 * 8, "one 8-byte unit of a tile per thread");
+#pragma unroll
+  for (int run = 0; run < 4 / R; ++run) {
+    uint2* first = reinterpret_cast<uint2*>(slot + run * R * (kGbTL * 32)) + tid;
+    const uint2 v = *first;
+    float s0 = bf16_lo(v.x), s1 = bf16_hi(v.x), s2 = bf16_lo(v.y), s3 = bf16_hi(v.y);
+#pragma unroll
+    for (int q = 1; q < R; ++q) {
+      const uint2 o = *(reinterpret_cast<const uint2*>(slot + (run * R + q) * (kGbTL * 32)) + tid);
+      s0 += bf16_lo(o.x); s1 += bf16_hi(o.x); s2 += bf16_lo(o.y); s3 += bf16_hi(o.y);
+    }
+    *first = make_uint2(pack_bf16x2(s0, s1), pack_bf16x2(s2, s3));
+  }
+}
+
+// REDUCE: shared heads only - dB_logits / dC are summed over runs of this many neighbouring heads (1, 2 or 4).
+template <int STAGES, bool SHARED, int REDUCE = 1>
 __global__ void __launch_bounds__(128, 4)
 btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -176,7 +199,7 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
 
   const uint32_t frag_off = ((lane & 7) + 8 * (lane >> 4)) * 128 + (((2 * warp + ((lane >> 3) & 1)) ^ (lane & 7)) << 4);
   // the same block inside this warp's dense [TL][16 channels] tile (shared key/value heads)
-  const uint32_t kv_off = SHARED ? warp * (TL * 32) + ((lane & 7) + 8 * (lane >> 4)) * 32 + ((lane >> 3) & 1) * 16 : frag_off;
+  const uint32_t kv_off = SHARED ? warp * (TL * 32) + ((lane & 7) + 8 * (lane >> 4)) * 32 + ((((lane >> 3) ^ (lane >> 2)) & 1) << 4) : frag_off;
   constexpr uint32_t kKvBlock = SHARED ? 512 : 2048;  // bytes from one 16-token block to the next in the B / C tiles
 
   // ---- per chunk: tables T, P, Pshift, L15, S (one token per lane, 16 lanes per block)
@@ -312,13 +335,21 @@ btp_gated_backward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid
     fence_proxy_async_smem();
     __syncthreads();
     if constexpr (SHARED) {
-      // threads 0-3: the per-head dB tiles, 4-7: the per-head dC tiles (16 columns each of the [B, L, H*16]
-      // outputs), 8: the dV box; every storing thread keeps its own async group
+      constexpr int r = REDUCE;
+      if constexpr (REDUCE > 1) {
+        sum_head_tiles<REDUCE>(smem_raw + (0 * STAGES + p_stage) * kGbBox, tid);  // dB_logits
+        sum_head_tiles<REDUCE>(smem_raw + (1 * STAGES + p_stage) * kGbBox, tid);  // dC
+        fence_proxy_async_smem();
+        __syncthreads();
+      }
+      // threads 0-3: the dB tiles, 4-7: the dC tiles (16 columns each; only the first tile of every run of r heads
+      // leaves), 8: the dV box; every storing thread keeps its own async group
       if (tid < 9) {
         const int w = tid & 3;
         const uint64_t map = reinterpret_cast<uint64_t>(tid < 4 ? &tm_db : (tid < 8 ? &tm_dc : &tm_dv));
         const uint32_t from = tid < 8 ? io_addr(tid >> 2, p_stage) + w * (TL * 32) : io_addr(2, p_stage);
-        tma_store_3d(map, tid < 8 ? (p_hg * 4 + w) * 16 : p_hg * 64, p_c0, p_b, from);
+        if (tid == 8 || w % r == 0)
+          tma_store_3d(map, tid < 8 ? ((p_hg * 4 + w) / r) * 16 : p_hg * 64, p_c0, p_b, from);
         bulk_commit_group();
         if (issued < n) bulk_wait_group_read<1>();
       }

@@ -113,7 +113,7 @@ int make_map(CUtensorMap* map, const void* base, MapShape sh, long long rows, in
 }
 
 // Token-major tensor [B][L][cols] bf16 with row pitch `ld` elements; box = `box_rows` tokens x 64 channels.
-// `narrow`: box = `box_rows` tokens x 16 channels (one head), dense 32-byte rows without swizzle - the per-head
+// `narrow`: box = `box_rows` tokens x 16 channels (one head), dense 32-byte rows with the 32-byte swizzle - the per-head
 // tiles of the kernels that read shared key/value heads in place.
 int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, long long ld, int box_rows = 64,
                     bool narrow = false) {
@@ -124,7 +124,7 @@ int make_map_tokens(CUtensorMap* map, const void* base, int B, int L, int cols, 
   const cuuint32_t box[3] = {narrow ? 16u : 64u, static_cast<cuuint32_t>(box_rows), 1u};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, narrow ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, narrow ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(BTP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
   return BTP_OK;
@@ -472,7 +472,14 @@ int launch_gated_forward(const void* a_logits, const void* b_logits, const void*
 }
 
 // ------------------------------------------------------------------ gated backward launch
-template <bool SHARED>
+// Over how many neighbouring heads a CTA of the gated backward sums dB_logits / dC before storing them: the 4 heads
+// of a CTA share one key/value head when the group size is a multiple of 4, form two pairs when it is 2.
+int gated_backward_reduce(int H, int kv_heads) {
+  const int group = H / kv_heads;
+  return group % 4 == 0 ? 4 : (group == 2 ? 2 : 1);
+}
+
+template <bool SHARED, int REDUCE>
 int launch_gated_backward(const void* a_logits, const void* b_logits, const void* c, const void* v, const void* dout,
                           void* da_logits, void* db_logits, void* dc, void* dv, int B, int L, int H, int kv_heads,
                           long long ld_a, long long ld_b, long long ld_c, long long ld_v, long long ld_do, long long ld_da,
@@ -485,7 +492,7 @@ int launch_gated_backward(const void* a_logits, const void* b_logits, const void
   if (total > 0x7fffffffll) return fail(BTP_ERR_BAD_SHAPE, "%s: %lld work units exceed the 2^31-1 limit", fn, total);
   constexpr int STAGES = 3;
   using SM = GatedBwdSmem<STAGES>;
-  auto kern = btp_gated_backward_kernel<STAGES, SHARED>;
+  auto kern = btp_gated_backward_kernel<STAGES, SHARED, REDUCE>;
   static Launcher<decltype(kern)> LN(kern, SM::kBytes, 128);
   int dev;
   DeviceInfo info;
@@ -500,8 +507,9 @@ int launch_gated_backward(const void* a_logits, const void* b_logits, const void
   if ((rc = make_map_tokens(&tm_c, c, B, L, SHARED ? kcols : icols, ld_c, kGbTL, SHARED))) return rc;
   if ((rc = make_map_tokens(&tm_v, v, B, L, icols, ld_v, kGbTL))) return rc;
   if ((rc = make_map_tokens(&tm_do, dout, B, L, icols, ld_do, kGbTL))) return rc;
-  if ((rc = make_map_tokens(&tm_db, db_logits, B, L, icols, ld_db, kGbTL, SHARED))) return rc;
-  if ((rc = make_map_tokens(&tm_dc, dc, B, L, icols, ld_dc, kGbTL, SHARED))) return rc;
+  constexpr int reduce = REDUCE;
+  if ((rc = make_map_tokens(&tm_db, db_logits, B, L, icols / reduce, ld_db, kGbTL, SHARED))) return rc;
+  if ((rc = make_map_tokens(&tm_dc, dc, B, L, icols / reduce, ld_dc, kGbTL, SHARED))) return rc;
   if ((rc = make_map_tokens(&tm_dv, dv, B, L, icols, ld_dv, kGbTL))) return rc;
   const long long cap = static_cast<long long>(info.sms) * ctas;
   const int grid = static_cast<int>(total < cap ? total : cap);
@@ -683,7 +691,8 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
   if (kv_heads <= 0 || H % kv_heads != 0)
     return fail(BTP_ERR_BAD_SHAPE, "%s: kv_heads must divide the number of heads (got %d, %d)", fn, kv_heads, H);
   const long long cols = static_cast<long long>(H) * 16, kcols = static_cast<long long>(kv_heads) * 16;
-  if (ld_a < H || ld_da < H || ld_b < kcols || ld_c < kcols || ld_v < cols || ld_do < cols || ld_db < cols || ld_dc < cols ||
+  const long long gcols = cols / gated_backward_reduce(H, kv_heads);  // width of dB_logits and dC (see the header)
+  if (ld_a < H || ld_da < H || ld_b < kcols || ld_c < kcols || ld_v < cols || ld_do < cols || ld_db < gcols || ld_dc < gcols ||
       ld_dv < cols)
     return fail(BTP_ERR_BAD_SHAPE, "%s: a row pitch is smaller than its row", fn);
   if (ld_b % 8 || ld_c % 8 || ld_v % 8 || ld_do % 8 || ld_db % 8 || ld_dc % 8 || ld_dv % 8 || ld_da % 4)
@@ -691,11 +700,16 @@ int btp_sm100_gated_backward(const void* a_logits, const void* b_logits, const v
   if (misaligned(b_logits) || misaligned(c) || misaligned(v) || misaligned(dout) || misaligned(db_logits) || misaligned(dc) ||
       misaligned(dv) || (reinterpret_cast<uintptr_t>(a_logits) & 1u) || (reinterpret_cast<uintptr_t>(da_logits) & 7u))
     return fail(BTP_ERR_MISALIGNED, "%s: the [B,L,H*16] tensors must be 16-byte aligned, dA_logits 8-byte aligned", fn);
-  if (kv_heads < H)
-    return launch_gated_backward<true>(a_logits, b_logits, c, v, dout, da_logits, db_logits, dc, dv, B, L, H, kv_heads, ld_a,
-                                       ld_b, ld_c, ld_v, ld_do, ld_da, ld_db, ld_dc, ld_dv, k, stream);
-  return launch_gated_backward<false>(a_logits, b_logits, c, v, dout, da_logits, db_logits, dc, dv, B, L, H, kv_heads, ld_a,
-                                      ld_b, ld_c, ld_v, ld_do, ld_da, ld_db, ld_dc, ld_dv, k, stream);
+#define BTP_GATED_BWD(SHARED, REDUCE)                                                                                  \
+  launch_gated_backward<SHARED, REDUCE>(a_logits, b_logits, c, v, dout, da_logits, db_logits, dc, dv, B, L, H, kv_heads, \
+                                        ld_a, ld_b, ld_c, ld_v, ld_do, ld_da, ld_db, ld_dc, ld_dv, k, stream)
+  if (kv_heads == H) return BTP_GATED_BWD(false, 1);
+  switch (gated_backward_reduce(H, kv_heads)) {
+    case 4: return BTP_GATED_BWD(true, 4);
+    case 2: return BTP_GATED_BWD(true, 2);
+    default: return BTP_GATED_BWD(true, 1);
+  }
+#undef BTP_GATED_BWD
 }
 
 int btp_sm100_decode_step(const void* a_t, const void* x_t, const void* c_t, const void* v_t, void* y_t,

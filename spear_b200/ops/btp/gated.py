@@ -61,6 +61,13 @@ def _kv_heads(b_logits: torch.Tensor, c: torch.Tensor, H: int) -> int:
     return kv
 
 
+def _shared_run(H: int, kv: int) -> int:
+    """Over how many neighbouring heads the backward kernel itself sums dB_logits and dC: 4 when the group size
+    H / kv is a multiple of 4 (the four heads of a CTA share one key/value head), 2 when it is 2, else 1."""
+    group = H // kv
+    return 4 if group % 4 == 0 else (2 if group == 2 else 1)
+
+
 def _launch_forward(a_logits, b_logits, c, v, out, k: int) -> None:
     _same_batch_and_length(a_logits, ((b_logits, "b_logits"), (c, "c"), (v, "v"), (out, "out")))
     B, L, H = a_logits.shape
@@ -99,8 +106,9 @@ def _launch_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, k: int) -> 
     kv = _kv_heads(b_logits, c, H)
     ld = [_rows(a_logits, H, "a_logits"), _rows(b_logits, kv * 16, "b_logits"), _rows(c, kv * 16, "c"),
           _rows(v, cols, "v"), _rows(dout, cols, "dout")]
-    # db and dc are per head even when the inputs are shared: the caller sums them over the heads of a group
-    ld += [_rows(da, H, "da_logits")] + [_rows(t, cols, n) for t, n in ((db, "db_logits"), (dc, "dc"), (dv, "dv"))]
+    # db and dc come out summed over the runs of heads that a CTA shares (see _shared_run): width H*16 / run
+    gcols = cols // _shared_run(H, kv)
+    ld += [_rows(da, H, "da_logits"), _rows(db, gcols, "db_logits"), _rows(dc, gcols, "dc"), _rows(dv, cols, "dv")]
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     with _native._OnDevice(v.device.index) as stream:
         rc = _lib.load().btp_sm100_gated_backward(p(a_logits), p(b_logits), p(c), p(v), p(dout), p(da), p(db), p(dc), p(dv),
@@ -145,13 +153,16 @@ def _backward(a_logits, b_logits, c, v, dout, k):
     B, L, H = a_logits.shape
     cols = H * 16
     dout = dout if dout.stride(2) == 1 else dout.contiguous()
-    da = torch.empty(B, L, H, device=v.device, dtype=v.dtype)
-    db, dc, dv = (torch.empty(B, L, cols, device=v.device, dtype=v.dtype) for _ in range(3))
-    torch.ops.spear_btp.gated_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, int(k))
     kv = b_logits.shape[2] // 16
-    if kv < H:  # heads share key/value heads: the gradient of a shared head is the sum over its group
-        db = db.view(B, L, kv, H // kv, 16).sum(dim=3).reshape(B, L, kv * 16)
-        dc = dc.view(B, L, kv, H // kv, 16).sum(dim=3).reshape(B, L, kv * 16)
+    run = _shared_run(H, kv)
+    da = torch.empty(B, L, H, device=v.device, dtype=v.dtype)
+    dv = torch.empty(B, L, cols, device=v.device, dtype=v.dtype)
+    db, dc = (torch.empty(B, L, cols // run, device=v.device, dtype=v.dtype) for _ in range(2))
+    torch.ops.spear_btp.gated_backward(a_logits, b_logits, c, v, dout, da, db, dc, dv, int(k))
+    parts = H // kv // run  # partial sums per key/value head that the kernel left (1: nothing left to add)
+    if parts > 1:
+        db = db.view(B, L, kv, parts, 16).sum(dim=3).reshape(B, L, kv * 16)
+        dc = dc.view(B, L, kv, parts, 16).sum(dim=3).reshape(B, L, kv * 16)
     return da, db, dc, dv
 
 

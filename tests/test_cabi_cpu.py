@@ -116,7 +116,8 @@ def test_gated_entry_points_check_their_arguments(lib):
     assert fwd(kv=3) == -2 and "kv_heads must divide" in lib.btp_sm100_last_error().decode()
     assert fwd(kv=0) == -2 and bwd(kv=3) == -2
     assert fwd(kv=2, ld=(4, 24, 32, 64, 64)) == -2   # shared heads: B_logits row narrower than kv_heads*16
-    assert bwd(kv=2, ld=(4, 32, 32, 64, 64, 4, 32, 64, 64)) == -2   # dB_logits stays per head: pitch >= H*16
+    assert bwd(kv=2, ld=(4, 32, 32, 64, 64, 4, 24, 64, 64)) == -2   # groups of 2 are summed in the kernel: dB_logits has H*16/2 columns
+    assert bwd(kv=2, ld=(4, 32, 32, 64, 64, 4, 32, 32, 64)) != -2   # ... and a pitch of exactly that passes the shape checks
 
     assert fwd(H=6) == -2 and "multiple of 4" in lib.btp_sm100_last_error().decode()
     assert fwd(L=24) == -2
