@@ -434,7 +434,7 @@ def main():
         torch.cuda.empty_cache()
         n_x = max(20, nk // 2)
 
-        def plain_pair(nb, heads, length, coeff, log_coeff):
+        def plain_pair(nb, heads, length, coeff, log_coeff, forward_only=False):
             ss = make_sets(nb, heads, length, 2, coeff)
 
             def f(i):
@@ -449,7 +449,8 @@ def main():
                 f(i)
                 b(i)
 
-            r = [statistics.median(loop_us(fn, n_x, 3)) for fn in (f, b, fb)]
+            r = [statistics.median(loop_us(fn, n_x, 3)) for fn in ((f,) if forward_only else (f, b, fb))]
+            r.extend(_lib.last_launch())  # CTAs and cluster size of the last launch (the forward's when forward_only)
             del ss
             torch.cuda.empty_cache()
             return r
@@ -463,13 +464,21 @@ def main():
         del cs
         torch.cuda.empty_cache()
         # configs[3]: long sequences, near-unit decays given as float32 log a (4 more bytes per head-token)
-        f3, b3, s3 = over_ranks_max(plain_pair(16, 64, 8192, "f32log", True))
+        f3, b3, s3 = over_ranks_max(plain_pair(16, 64, 8192, "f32log", True)[:3])
+        # the same forward with the carry handed over between CTAs of a cluster instead of recomputed at the seams
+        f3r, grid_r, _ = plain_pair(16, 64, 8192, "f32log", True, forward_only=True)
+        _lib.set_seam_mode(_lib.SEAM_HANDOFF)
+        try:
+            f3h, grid_h, cluster_h = plain_pair(16, 64, 8192, "f32log", True, forward_only=True)
+        finally:
+            _lib.set_seam_mode(_lib.SEAM_RECOMPUTE)
+        f3r, f3h = over_ranks_max([f3r, f3h])
         # the BTP part of configs[4] (Phalanx layer, dim 2048, L 2048, global batch 64) in the plain layout
         nb4 = 64
-        f4, b4, s4 = over_ranks_max(plain_pair(nb4, 128, 2048, "bf16", False))
+        f4, b4, s4 = over_ranks_max(plain_pair(nb4, 128, 2048, "bf16", False)[:3])
         # strong scaling of the headline workload: the global batch of 1024 split over the ranks
         lo, hi = batch_shard(1024, rank, world)
-        fs, bs, ss_ = over_ranks_max(plain_pair(hi - lo, H, L, "bf16", False))
+        fs, bs, ss_ = over_ranks_max(plain_pair(hi - lo, H, L, "bf16", False)[:3])
         _lib.device_status()
         extra = {"world": world, "loop": f"{n_x} launches between two CUDA events, median of 3, slowest rank; 2 rotating sets"}
 
@@ -486,6 +495,11 @@ def main():
             "us_per_launch": copy_us, "gbs": copy_bytes / copy_us / 1e3}
         extra["configs3"] = cfg_line("btp fwd+bwd B=16 H=64 L=8192 per GPU, float32 log a ~ U(-1e-3,0), bf16 x/dy",
                                      16, 64, 8192, FWD_BYTES_PER_HT + 2, BWD_BYTES_PER_HT + 2, f3, b3, s3)
+        extra["configs3"]["seam"] = {
+            "what": "forward alone, the carry across the seams between warps' stretches recomputed from the block to the "
+                    "left (default) against handed over through distributed shared memory in a thread-block cluster",
+            "recompute_fwd_us": f3r, "recompute_grid": grid_r,
+            "handoff_fwd_us": f3h, "handoff_grid": grid_h, "handoff_cluster": cluster_h}
         extra["configs4_btp_part"] = cfg_line("btp fwd+bwd B=64 H=128 L=2048 per GPU, bf16 (plain layout)",
                                               nb4, 128, 2048, FWD_BYTES_PER_HT, BWD_BYTES_PER_HT, f4, b4, s4)
         extra["strong_scaling"] = {

@@ -220,6 +220,31 @@ int btp_sm100_device_status(void* stream, unsigned int* detail);
 unsigned long long btp_sm100_set_wait_limit(unsigned long long ns);
 
 /*
+ * How the forward kernel gets the carry across a seam, i.e. where the stretch of a sequence one warp works on ends
+ * and another warp's begins (sequences longer than 256 tokens; the result is the same to rounding either way):
+ *   BTP_SEAM_RECOMPUTE (default)  the warp on the right re-reads the one 16-token block to its left and recomputes
+ *                                 the 16 numbers; no warp ever waits for another.
+ *   BTP_SEAM_HANDOFF              the warp on the left hands the 16 numbers over through distributed shared memory
+ *                                 inside a thread-block cluster, which is what the reference does between the CTAs
+ *                                 of its cluster (csrc/btp/btp-forward.cu:276-335, csrc/btp/btp_common.h:56-64).
+ *                                 Taken for k = 2, a 16-bit y without checkpoint, L a multiple of 128 and 2 ... 32
+ *                                 stretches per sequence (a power of two); every other call recomputes.
+ * Applies to every forward launch that follows, process-wide.  Returns the previous mode; any other value of
+ * `mode` changes nothing and returns the current mode.
+ */
+#define BTP_SEAM_RECOMPUTE 0
+#define BTP_SEAM_HANDOFF 1
+int btp_sm100_set_seam_mode(int mode);
+
+/*
+ * Launch shape of the last btp_sm100_forward / btp_sm100_backward kernel the CALLING THREAD launched: the number of
+ * CTAs and the thread-block cluster size (1 unless BTP_SEAM_HANDOFF applied).  Either pointer may be NULL.  A
+ * diagnostic with no counterpart in the reference; the hand-off's grid is one wave of resident clusters, which is
+ * fewer CTAs than the device holds without clusters.
+ */
+void btp_sm100_last_launch(int* grid, int* cluster);
+
+/*
  * Test hook for the give-up path, no counterpart in the reference: the NEXT forward or backward launch makes
  * warp 0 of block 0 expect `bytes` more bytes on its first load barrier than its loads deliver, so that this
  * one wait runs out.  The kernel then behaves as documented for a timeout: it returns normally, the chunks of

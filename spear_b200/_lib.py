@@ -21,6 +21,9 @@ DTYPE_F32_LOG = 2
 DTYPE_F16 = 3
 ACT_F16 = 0x10  # flag on a float coefficient tag: the activations are float16
 
+SEAM_RECOMPUTE = 0  # forward: the carry across a seam is recomputed from the block to the left (default)
+SEAM_HANDOFF = 1    # forward: the carry is handed over through distributed shared memory inside a cluster
+
 ABI_VERSION = 3
 
 # every symbol include/btp_sm100.h declares: name -> (restype, argtypes)
@@ -35,6 +38,8 @@ SYMBOLS = {
     "btp_sm100_prefill_state": (_i, [_vp] * 5 + [_ll, _i, _i, _i, _i, _vp]),
     "btp_sm100_noalloc_read_record": (_i, [_vp, _ll, _vp]),
     "btp_sm100_set_wait_limit": (ctypes.c_ulonglong, [ctypes.c_ulonglong]),
+    "btp_sm100_set_seam_mode": (_i, [_i]),
+    "btp_sm100_last_launch": (None, [ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "btp_sm100_test_expect_missing_bytes": (None, [ctypes.c_uint]),
     "btp_sm100_status_string": (ctypes.c_char_p, [_i]),
     "btp_sm100_last_error": (ctypes.c_char_p, []),
@@ -92,6 +97,21 @@ def device_status(stream: int = 0) -> None:
     lib = load()
     detail = (ctypes.c_uint * 4)()
     check(lib.btp_sm100_device_status(ctypes.c_void_p(stream), detail), "btp_sm100_device_status")
+
+
+def set_seam_mode(mode: int) -> int:
+    """Selects how the forward kernel gets the carry across a seam (SEAM_RECOMPUTE, SEAM_HANDOFF); process-wide.
+    Returns the previous mode."""
+    if mode not in (SEAM_RECOMPUTE, SEAM_HANDOFF):
+        raise ValueError(f"seam mode must be SEAM_RECOMPUTE (0) or SEAM_HANDOFF (1), got {mode!r}")
+    return int(load().btp_sm100_set_seam_mode(mode))
+
+
+def last_launch() -> tuple[int, int]:
+    """(CTAs, cluster size) of the last forward/backward kernel this thread launched."""
+    g, c = _i(0), _i(0)
+    load().btp_sm100_last_launch(ctypes.byref(g), ctypes.byref(c))
+    return g.value, c.value
 
 
 def launch_count() -> int:

@@ -527,12 +527,56 @@ __device__ __forceinline__ void report_error(unsigned int code, int warp, int ch
   }
 }
 
+// Hand-off of the carry between the runs of one sequence (forward kernel, HANDOFF).
+//
+// Runs are dealt round-robin to the warps of the grid and the grid holds a whole number of sequences' worth of
+// warps, so a warp always works on run q = (its index) mod (runs per sequence) of some sequence, and the warps with
+// the neighbouring indices work on the neighbouring runs of the SAME sequence at the same time.  The launch puts the
+// warps of one sequence into one thread-block cluster, so a warp can write into its right neighbour's shared memory.
+//   * The carry into a run's first block is only needed for that block's OUTPUT (the carry is one hop: the next
+//     block takes the uncorrected last token).  The warp therefore runs through its run without it, keeps the first
+//     block's uncorrected result in registers, and corrects and stores that one block at the end of the run.
+//   * At the end of its run a warp has the uncorrected last token of the run in registers: exactly what the right
+//     neighbour is missing.  It stores the 16 numbers into the neighbour's landing slot (st.async counts the bytes
+//     on the neighbour's mbarrier), then waits (bounded) for its own slot to fill.
+//   * Two slots per warp, used alternately; before a slot is written a second time the writer waits (bounded) for the
+//     credit the reader sends when it has read the slot (an arrive on an mbarrier of the writer).
+// Per warp: 2 x 64 bytes of landing slots, 2 "slot full" barriers, 2 "credit" barriers.
+constexpr int kSeamBytesPerWarp = 2 * 64 + 2 * 8 + 2 * 8;
+struct SeamLink {
+  uint32_t slot;        // own landing slots (shared::cta address), 64 bytes each: [g][2] floats = channels g, g+8
+  uint32_t full;        // own "slot full" barriers
+  uint32_t credit;      // own credit barriers (the right neighbour arrives on them)
+  uint32_t right_slot;  // right neighbour's landing slots / "slot full" barriers, left neighbour's credit barriers
+  uint32_t right_full;  //   (cluster-wide shared addresses)
+  uint32_t left_credit;
+  __device__ __forceinline__ void set(uint32_t seam_base, int warp, int warps) {
+    const uint32_t rank = cluster_cta_rank();
+    const auto at = [&](int w) { return seam_base + static_cast<uint32_t>(w) * kSeamBytesPerWarp; };
+    slot = at(warp);
+    full = slot + 128;
+    credit = slot + 144;
+    const int rw = warp + 1 == warps ? 0 : warp + 1, lw = warp == 0 ? warps - 1 : warp - 1;
+    // a warp without a neighbour on that side never uses the address; its rank is clamped so that it stays mappable
+    const uint32_t last = cluster_cta_count() - 1;
+    const uint32_t rr = warp + 1 == warps ? (rank < last ? rank + 1 : rank) : rank;
+    const uint32_t lr = warp == 0 ? (rank > 0 ? rank - 1 : rank) : rank;
+    right_slot = map_to_cta(at(rw), rr);
+    right_full = right_slot + 128;
+    left_credit = map_to_cta(at(lw) + 144, lr);
+  }
+};
+
 // =====================================================================================
 // Forward
 // =====================================================================================
 // PRECISE: Lmat goes to the tensor cores as two bf16 terms (see build_lmat_split).
 // F16: activations (x, y, a 16-bit coefficient) are float16 instead of bfloat16.
-template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16 = false>
+// HANDOFF: the carry that crosses the seam between two runs of a sequence is handed from the warp that owns the
+// left run to the warp that owns the right one through (distributed) shared memory instead of being recomputed
+// from a halo block; see SeamLink.  The kernel is then launched in clusters of runs_per_sequence / WARPS CTAs.
+template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16 = false,
+          bool HANDOFF = false>
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const __grid_constant__ CUtensorMap tm_c, const KernelParams p) {
@@ -554,15 +598,31 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const long long wid = static_cast<long long>(blockIdx.x) * WARPS + warp;
   RunCursor cons;
   const int n = forward_work(wid, nwarps, p, cons);
-  if (n <= 0) return;
-  if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled boxes need a 1024-byte aligned base
-    if (lane == 0) report_error(2u, warp, 0);
+  static_assert(!HANDOFF || (!OUT_F32 && !CKPT && !RAGGED), "the hand-off variant covers full chunks and 16-bit outputs");
+  SeamLink seam;
+  if constexpr (HANDOFF) seam.set(smem_u32(smem_raw) + LAYOUT::kBytes, warp, WARPS);
+  // With HANDOFF every thread of the cluster passes two cluster-wide barriers: one after the barriers are
+  // initialised (nobody writes into a CTA that has not set up yet), one before leaving (nobody leaves while a
+  // neighbour may still write into its shared memory).  A warp without work passes both right away.
+  if (n <= 0 || (smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled boxes need a 1024-byte aligned base
+    if (n > 0 && lane == 0) report_error(2u, warp, 0);
+    if constexpr (HANDOFF) {
+      cluster_sync_all();
+      cluster_sync_all();
+    }
     return;
   }
 
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) mbar_init(ws.bar(s), 1);
+    if constexpr (HANDOFF) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        mbar_init(seam.full + 8 * s, 1);
+        mbar_init(seam.credit + 8 * s, 1);
+      }
+    }
     mbar_init_fence();
     fence_proxy_async_smem();
     prefetch_tensormap(&tm_x);
@@ -572,6 +632,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (p.test_missing_tx != 0 && blockIdx.x == 0 && warp == 0) mbar_expect_tx(ws.bar(0), p.test_missing_tx);
   }
   __syncwarp();
+  if constexpr (HANDOFF) cluster_sync_all();
   pdl_wait();  // nothing above touches global memory; everything below may read what the previous kernel wrote
 
   const int L = p.L, ncs = p.ncs;
@@ -602,6 +663,12 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   bool failed = false;
   int j = 0, s = 0;
   uint32_t phase = 0;
+  // HANDOFF: the run in work is this warp's krun-th; its first block waits, uncorrected, for the carry from the left
+  int krun = 0;
+  bool owed = false;
+  float f0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, f1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float2 fPa = make_float2(0.0f, 0.0f), fPb = fPa;
+  unsigned short* fy = nullptr;
 
   for (; j < n; ++j) {
     if (j + AHEAD < n) {
@@ -621,7 +688,14 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
     } else if (cons.fresh) {  // the block to the left belongs to another warp (or another run)
-      halo_reduce<COEF, false, false, PRECISE, F16>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
+      if constexpr (HANDOFF) {
+        cg = cg8 = 0.0f;
+        owed = true;
+        fy = reinterpret_cast<unsigned short*>(p.out_f32) + (static_cast<long long>(cons.bh) * 16 + tl.g) * L + c0 + 2 * tl.t;
+        if (lane == 0) mbar_arrive_expect_tx(seam.full + 8 * (krun & 1), 64);
+      } else {
+        halo_reduce<COEF, false, false, PRECISE, F16>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, cg, cg8);
+      }
     }
 
     const float* tg = tab + tl.g;
@@ -671,6 +745,17 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const float2 yd = __ffma2_rn(Pb, cg82, make_float2(v1[2], v1[3]));
         const float y0[4] = {ya.x, ya.y, yb.x, yb.y};
         const float y1[4] = {yc.x, yc.y, yd.x, yd.y};
+        if constexpr (HANDOFF) {
+          if (i == 0 && cons.fresh) {  // kept for the correction at the end of the run
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              f0[e] = v0[e];
+              f1[e] = v1[e];
+            }
+            fPa = Pa;
+            fPb = Pb;
+          }
+        }
         if constexpr (CKPT) {
           // slot j of the checkpoint = block-local last token of block j, except the last block
           if (p.use_carry && tl.t == 3 && (cons.cs * NT + i) < (L >> 4) - 1) {
@@ -708,6 +793,47 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         bulk_commit_group();
       }
     }
+    if constexpr (HANDOFF) {
+      if (cons.left == 1) {  // end of a run
+        const int sl = krun & 1;
+        const uint32_t use = static_cast<uint32_t>(krun >> 1);
+        if (p.use_carry && cons.cs != ncs - 1) {  // the run to the right is waiting for (cg, cg8)
+          bool ok = true;
+          if (krun >= 2) ok = mbar_wait_bounded_cluster(seam.credit + 8 * sl, (use - 1) & 1u, p.wait_limit_ns);
+          if (!__all_sync(0xffffffffu, ok)) {
+            failed = true;
+            break;
+          }
+          if (tl.t == 0) st_async_f32x2(seam.right_slot + 64 * sl + 8 * tl.g, cg, cg8, seam.right_full + 8 * sl);
+        }
+        if (owed) {
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded_cluster(seam.full + 8 * sl, use & 1u, p.wait_limit_ns))) {
+            failed = true;
+            break;
+          }
+          float c_g, c_g8;
+          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(c_g), "=f"(c_g8) : "r"(seam.slot + 64 * sl + 8 * tl.g) : "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive_remote(seam.left_credit + 8 * sl);
+          // The run's first chunk left through a TMA store with this block uncorrected.  A run has at least two
+          // chunks, so when all store groups but the latest are complete, that store is.
+          if (lane < NBOX) bulk_wait_group<1>();
+          __syncwarp();
+          const float2 cc = make_float2(c_g, c_g), cc8 = make_float2(c_g8, c_g8);
+          const float2 ya = __ffma2_rn(fPa, cc, make_float2(f0[0], f0[1]));
+          const float2 yb = __ffma2_rn(fPa, cc8, make_float2(f0[2], f0[3]));
+          const float2 yc = __ffma2_rn(fPb, cc, make_float2(f1[0], f1[1]));
+          const float2 yd = __ffma2_rn(fPb, cc8, make_float2(f1[2], f1[3]));
+          const long long r8 = 8ll * L;
+          *reinterpret_cast<uint32_t*>(fy) = Act<F16>::pack(ya.x, ya.y);
+          *reinterpret_cast<uint32_t*>(fy + r8) = Act<F16>::pack(yb.x, yb.y);
+          *reinterpret_cast<uint32_t*>(fy + 8) = Act<F16>::pack(yc.x, yc.y);
+          *reinterpret_cast<uint32_t*>(fy + 8 + r8) = Act<F16>::pack(yd.x, yd.y);
+          owed = false;
+        }
+        ++krun;
+      }
+    }
     cons.next(ncs);
     if (++s == STAGES) {
       s = 0;
@@ -727,6 +853,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   }
   if (!OUT_F32 && lane < NBOX) bulk_wait_group<0>();
+  if constexpr (HANDOFF) cluster_sync_all();
 }
 
 // =====================================================================================

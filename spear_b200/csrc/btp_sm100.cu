@@ -23,6 +23,8 @@ thread_local char tls_error[512] = "";
 std::atomic<unsigned long long> g_launches{0};
 std::atomic<unsigned long long> g_wait_limit_ns{btp::kWaitLimitNs};  // btp_sm100_set_wait_limit
 std::atomic<unsigned int> g_test_missing_tx{0};                      // btp_sm100_test_expect_missing_bytes, one launch
+std::atomic<int> g_seam_mode{BTP_SEAM_RECOMPUTE};                    // btp_sm100_set_seam_mode
+thread_local int tls_last_grid = 0, tls_last_cluster = 0;            // btp_sm100_last_launch
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -276,10 +278,98 @@ int forward_run_len(const Dims& d, long long nwarps) {
 
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
+// ------------------------------------------------------------------ forward with the carry handed over between CTAs
+// (BTP_SEAM_HANDOFF; see SeamLink in btp_kernels.cuh).  Applies when the forward would deal runs of at least two
+// chunks, 2 ... 32 of them per sequence (a power of two): the warps of one sequence then form one cluster of
+// runs_per_sequence / WARPS CTAs (1, 2, 4 or 8).  Returns BTP_OK with *done = false when the shape does not qualify
+// and the caller has to take the recomputing kernel.
+template <int COEF, bool F16>
+int launch_forward_handoff(const void* coeff, const void* x, void* y, Dims d, cudaStream_t stream, bool* done) {
+  constexpr int NBOX = 2, STAGES = 3, WARPS = 4;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
+  constexpr int kSmem = LAYOUT::kBytes + WARPS * kSeamBytesPerWarp;
+  auto kern = btp_forward_kernel<COEF, false, false, false, true, NBOX, STAGES, WARPS, F16, true>;
+  static Launcher<decltype(kern)> L(kern, kSmem, WARPS * 32);
+  *done = false;
+  int dev;
+  DeviceInfo info;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  int ctas;
+  if ((rc = L.prepare(dev, &ctas))) return rc;
+  if ((rc = set_chunks("btp_sm100_forward", &d, LAYOUT::kTL))) return rc;
+  // the run length the recomputing kernel would take on the full grid decides, so that both walk memory alike
+  const int run_len = forward_run_len(d, static_cast<long long>(info.sms) * ctas * WARPS);
+  if (run_len < 2 || run_len >= d.ncs) return BTP_OK;
+  const int rps = d.ncs / run_len;
+  if (rps > 32 || (rps & (rps - 1)) != 0) return BTP_OK;
+  const int cluster = rps > WARPS ? rps / WARPS : 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  // The grid is one wave: as many clusters as the device holds at once (fewer than SMs x CTAs per SM / cluster size
+  // when the SMs of a GPC do not divide into clusters), asked once per device and cluster size.
+  static int resident[64][4];  // [device][log2 cluster size], 0 = not asked yet
+  static std::mutex resident_mu;
+  const int slot = cluster == 1 ? 0 : cluster == 2 ? 1 : cluster == 4 ? 2 : 3;
+  int clusters = 0;
+  {
+    std::lock_guard<std::mutex> lock(resident_mu);
+    if (resident[dev][slot] == 0) {
+      cfg.gridDim = dim3(static_cast<unsigned>(info.sms * ctas / cluster * cluster));
+      cfg.numAttrs = 1;
+      int n = 0;
+      BTP_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      if (n < 1) return fail(BTP_ERR_CUDA, "no cluster of %d CTAs fits on device %d", cluster, dev);
+      resident[dev][slot] = n;
+    }
+    clusters = resident[dev][slot];
+  }
+  // a whole number of clusters; every warp of the grid has work (there are at least 4 runs per warp of the full grid)
+  int grid = L.grid_for(info.sms, ctas, d.total_chunks / run_len);
+  if (grid > clusters * cluster) grid = clusters * cluster;
+  grid -= grid % cluster;
+  if (grid < cluster) return BTP_OK;
+  CUtensorMap tm_x, tm_y, tm_c;
+  if ((rc = make_map(&tm_x, x, kActBf16, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_y, y, kActBf16, d.BH * 16, d.L))) return rc;
+  if ((rc = make_map(&tm_c, coeff, row_shape(CoefTraits<COEF>::kBytes, LAYOUT::kTL), d.BH, d.L))) return rc;
+  KernelParams p{};
+  p.coeff = coeff; p.x = x; p.out_f32 = y;
+  p.L = d.L; p.ncs = d.ncs; p.total_chunks = d.total_chunks; p.use_carry = 1;
+  p.run_len = run_len;
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.numAttrs = use_pdl() ? 2 : 1;
+  BTP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_y, tm_c, p));
+  tls_last_grid = grid;
+  tls_last_cluster = cluster;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  *done = true;
+  return BTP_OK;
+}
+
 // ------------------------------------------------------------------ forward dispatch
 template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16>
 int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
+  if constexpr (!OUT_F32 && !CKPT && !RAGGED && PRECISE && NBOX == 2 && STAGES == 3 && WARPS == 4) {
+    if (k == 2 && g_seam_mode.load(std::memory_order_relaxed) == BTP_SEAM_HANDOFF) {
+      bool done = false;
+      const int rc = launch_forward_handoff<COEF, F16>(coeff, x, y, d, stream, &done);
+      if (rc || done) return rc;
+    }
+  }
   auto kern = btp_forward_kernel<COEF, OUT_F32, CKPT, RAGGED, PRECISE, NBOX, STAGES, WARPS, F16>;
   static Launcher<decltype(kern)> L(kern, LAYOUT::kBytes, WARPS * 32);
   int dev;
@@ -306,6 +396,8 @@ int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, 
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
   BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_y, tm_c, p));
+  tls_last_grid = grid;
+  tls_last_cluster = 1;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
 }
@@ -393,6 +485,8 @@ int launch_backward_impl(const void* coeff, const void* x, const void* dy, void*
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   p.test_missing_tx = g_test_missing_tx.exchange(0u, std::memory_order_relaxed);
   BTP_CUDA_TRY(launch_kernel(kern, grid, WARPS * 32, LAYOUT::kBytes, stream, tm_x, tm_dy, tm_dx, tm_c, tm_da, p));
+  tls_last_grid = grid;
+  tls_last_cluster = 1;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return BTP_OK;
 }
@@ -798,6 +892,16 @@ int btp_sm100_noalloc_read_record(float* dst, long long n_floats, void* stream) 
 
 unsigned long long btp_sm100_set_wait_limit(unsigned long long ns) {
   return g_wait_limit_ns.exchange(ns ? ns : btp::kWaitLimitNs, std::memory_order_relaxed);
+}
+
+int btp_sm100_set_seam_mode(int mode) {
+  if (mode != BTP_SEAM_RECOMPUTE && mode != BTP_SEAM_HANDOFF) return g_seam_mode.load(std::memory_order_relaxed);
+  return g_seam_mode.exchange(mode, std::memory_order_relaxed);
+}
+
+void btp_sm100_last_launch(int* grid, int* cluster) {
+  if (grid) *grid = tls_last_grid;
+  if (cluster) *cluster = tls_last_cluster;
 }
 
 void btp_sm100_test_expect_missing_bytes(unsigned int bytes) { g_test_missing_tx.store(bytes, std::memory_order_relaxed); }
