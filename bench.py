@@ -226,6 +226,8 @@ def main():
     ap.add_argument("--coeff", default="bf16", choices=["bf16", "f32log"],
                     help="bf16: a = exp(-softplus(N(0,1))) in bf16; f32log: log a ~ U(-1e-3, 0) in float32")
     ap.add_argument("--sets", type=int, default=3, help="rotating input/output sets")
+    ap.add_argument("--seam", default="recompute", choices=["recompute", "handoff"],
+                    help="how the forward gets the carry across the seams between warps' stretches of a long sequence")
     ap.add_argument("--kernel-launches", type=int, default=200, help="launches per per-kernel timing loop")
     ap.add_argument("--kernel-repeats", type=int, default=5, help="repeats of each per-kernel timing loop")
     args = ap.parse_args()
@@ -262,6 +264,8 @@ def main():
     from spear_b200.sharding import batch_shard, bind_to_gpu_numa_node, max_over_ranks, sum_over_ranks
 
     _lib.load()
+    if args.seam == "handoff":
+        _lib.set_seam_mode(_lib.SEAM_HANDOFF)
     dev = torch.device("cuda", local_rank)
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
 
@@ -464,6 +468,7 @@ def main():
         del cs
         torch.cuda.empty_cache()
         # configs[3]: long sequences, near-unit decays given as float32 log a (4 more bytes per head-token)
+        _lib.set_seam_mode(_lib.SEAM_RECOMPUTE)  # the extras are quoted on the default kernels whatever --seam says
         f3, b3, s3 = over_ranks_max(plain_pair(16, 64, 8192, "f32log", True)[:3])
         # the same forward with the carry handed over between CTAs of a cluster instead of recomputed at the seams
         f3r, grid_r, _ = plain_pair(16, 64, 8192, "f32log", True, forward_only=True)
@@ -536,6 +541,7 @@ def main():
                 "workload": workload_string(),
                 "l2": f"each step touches {(fwd_b + bwd_b) * B * H * L / 1e6:.0f} MB (L2 holds 126 MB) and {NSETS} input/output sets rotate",
                 "parallelism": f"batch sharded over {world} GPU(s), no data-path collective",
+                "seam": args.seam,
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "per_gpu": e2e_value / world,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / max(1, args.e2e_steps),

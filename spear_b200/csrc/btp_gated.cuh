@@ -247,7 +247,7 @@ btp_gated_forward_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_
     const int c0 = cons.cs * TL;
     const int left = (L - c0) >> 4;
     const int nt = left < NT ? left : NT;
-    tables_from_log2<TL, false>(l2, tab, lane, carry_scale);
+    tables_from_log2<TL, false>(l2, tab, tab + TL, lane, carry_scale);
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
     } else if (j == 0) {

@@ -85,11 +85,14 @@ __device__ __forceinline__ float coef_log2(float a) {
 //   * STAGES buffers for the x tiles of a chunk (NBOX boxes of [16][64] bf16, 128-byte swizzled); a bf16
 //     output (y, dx) is written over them and leaves from there,
 //   * backward: STAGES-1 buffers for the dy tiles (they are dead as soon as the chunk's products are done),
-//   * STAGES landing zones for the raw coefficients, backward: STAGES staging rows for dA,
+//   * landing zones for the raw coefficients (backward: STAGES; forward: one more than the loads run ahead, the
+//     coefficients being consumed at the start of a chunk), backward: STAGES staging rows for dA,
 //   * the per-token float tables of the chunk in work (forward: T, P; backward, double-buffered because a
-//     chunk's last block is finished one block into the next chunk: T, Pshift, L15),
+//     chunk's last block is finished one block into the next chunk: T, Pshift, L15).  Forward with float
+//     coefficients: the T table is written over the chunk's raw coefficients (same size), which is what lets four
+//     CTAs of that kernel share an SM,
 //   * STAGES mbarriers.
-template <int COEF, int NBOX, int STAGES, int WARPS, bool BWD, bool DY_F32>
+template <int COEF, int NBOX, int STAGES, int WARPS, bool BWD, bool DY_F32, bool OUT_F32 = false>
 struct SmemLayout {
   static constexpr int kTL = 64 * NBOX;                 // tokens per chunk
   static constexpr int kTiles = kTL / 16;               // 16-token blocks per chunk
@@ -99,9 +102,11 @@ struct SmemLayout {
   static constexpr int kBigPerWarp = STAGES * kXBytes + kDyStages * kDyBytes;  // multiple of 1024 (swizzle atom)
   static constexpr int kRawBytes = kTL * CoefTraits<COEF>::kBytes;
   static constexpr int kDaBytes = BWD ? kTL * 4 : 0;
-  static constexpr int kTabFloats = (BWD ? 3 : 2) * kTL;
+  static constexpr int kRawStages = BWD ? STAGES : (OUT_F32 ? STAGES : STAGES - 1);
+  static constexpr bool kTInPlace = !BWD && COEF != kCoefBf16;
+  static constexpr int kTabFloats = (BWD ? 3 : (kTInPlace ? 1 : 2)) * kTL;
   static constexpr int kTabSets = BWD ? 2 : 1;
-  static constexpr int kSmallPerWarp = STAGES * (kRawBytes + kDaBytes) + kTabSets * kTabFloats * 4;
+  static constexpr int kSmallPerWarp = kRawStages * kRawBytes + STAGES * kDaBytes + kTabSets * kTabFloats * 4;
   static constexpr int kBarsPerWarp = STAGES * 8;
   static constexpr int kBytes = WARPS * (kBigPerWarp + kSmallPerWarp + kBarsPerWarp);
 };
@@ -114,13 +119,16 @@ struct WarpSmem {
   __device__ __forceinline__ uint32_t x(int s) const { return big + s * LAYOUT::kXBytes; }
   __device__ __forceinline__ uint32_t dy(int d) const { return big + STAGES * LAYOUT::kXBytes + d * LAYOUT::kDyBytes; }
   __device__ __forceinline__ uint32_t raw_addr(int s) const { return small + s * LAYOUT::kRawBytes; }
-  __device__ __forceinline__ const void* raw_ptr(int s) const { return small_ptr + s * LAYOUT::kRawBytes; }
-  __device__ __forceinline__ uint32_t da_addr(int s) const { return small + STAGES * LAYOUT::kRawBytes + s * LAYOUT::kDaBytes; }
+  __device__ __forceinline__ void* raw_ptr(int s) const { return small_ptr + s * LAYOUT::kRawBytes; }
+  __device__ __forceinline__ uint32_t da_addr(int s) const {
+    return small + LAYOUT::kRawStages * LAYOUT::kRawBytes + s * LAYOUT::kDaBytes;
+  }
   __device__ __forceinline__ float* da_ptr(int s) const {
-    return reinterpret_cast<float*>(small_ptr + STAGES * LAYOUT::kRawBytes + s * LAYOUT::kDaBytes);
+    return reinterpret_cast<float*>(small_ptr + LAYOUT::kRawStages * LAYOUT::kRawBytes + s * LAYOUT::kDaBytes);
   }
   __device__ __forceinline__ float* tab_ptr(int set) const {
-    return reinterpret_cast<float*>(small_ptr + STAGES * (LAYOUT::kRawBytes + LAYOUT::kDaBytes) + set * LAYOUT::kTabFloats * 4);
+    return reinterpret_cast<float*>(small_ptr + LAYOUT::kRawStages * LAYOUT::kRawBytes + STAGES * LAYOUT::kDaBytes +
+                                    set * LAYOUT::kTabFloats * 4);
   }
   __device__ __forceinline__ uint32_t bar(int s) const { return bars + s * 8; }
 };
@@ -281,8 +289,10 @@ __device__ __forceinline__ int chunk_tiles(int cs, int L) {
 // `carry_scale` is 1 (k = 2) or 0 (k = 1): every use of the carry and of the gradient that flows back
 // through it is multiplied by an entry of the P / Pshift table, so zeroing that table switches the one-hop
 // term off without a single extra instruction per block.
+// Destinations: tab = T; tab2 = the second table; the third (backward only) follows the second.
 template <int TL, bool BWD>
-__device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], float* tab, int lane, float carry_scale) {
+__device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], float* tab, float* tab2, int lane,
+                                                 float carry_scale) {
   constexpr int TPL = TL / 32;    // tokens per lane: 1, 2 or 4
   constexpr int LPT = 16 / TPL;   // lanes per block: 16, 8 or 4
   float T[TPL];
@@ -325,23 +335,25 @@ __device__ __forceinline__ void tables_from_log2(const float (&l2)[TL / 32], flo
   __syncwarp();  // nobody still reads the tables of the chunk before
   if constexpr (TPL == 4) {
     reinterpret_cast<float4*>(tab)[lane] = make_float4(T[0], T[1], T[2], T[3]);
-    reinterpret_cast<float4*>(tab + TL)[lane] = make_float4(second[0], second[1], second[2], second[3]);
-    if constexpr (BWD) reinterpret_cast<float4*>(tab + 2 * TL)[lane] = make_float4(third[0], third[1], third[2], third[3]);
+    reinterpret_cast<float4*>(tab2)[lane] = make_float4(second[0], second[1], second[2], second[3]);
+    if constexpr (BWD) reinterpret_cast<float4*>(tab2 + TL)[lane] = make_float4(third[0], third[1], third[2], third[3]);
   } else if constexpr (TPL == 2) {
     reinterpret_cast<float2*>(tab)[lane] = make_float2(T[0], T[1]);
-    reinterpret_cast<float2*>(tab + TL)[lane] = make_float2(second[0], second[1]);
-    if constexpr (BWD) reinterpret_cast<float2*>(tab + 2 * TL)[lane] = make_float2(third[0], third[1]);
+    reinterpret_cast<float2*>(tab2)[lane] = make_float2(second[0], second[1]);
+    if constexpr (BWD) reinterpret_cast<float2*>(tab2 + TL)[lane] = make_float2(third[0], third[1]);
   } else {
     tab[lane] = T[0];
-    tab[TL + lane] = second[0];
-    if constexpr (BWD) tab[2 * TL + lane] = third[0];
+    tab2[lane] = second[0];
+    if constexpr (BWD) tab2[TL + lane] = third[0];
   }
   __syncwarp();
 }
 
-// Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables at `tab`.
+// Once per chunk: raw coefficients (already in shared memory at `rawp`) -> per-token tables: T at `tab`, the others
+// from `tab2` on.  `tab` may be `rawp` itself when the coefficients are floats: a lane reads exactly the elements it
+// writes, and reads them first.
 template <int COEF, int TL, bool BWD, bool F16 = false>
-__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int lane, float carry_scale) {
+__device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, float* tab2, int lane, float carry_scale) {
   constexpr int TPL = TL / 32;  // tokens per lane: 2 or 4
   float v[TPL];
   if constexpr (COEF == kCoefBf16) {
@@ -364,7 +376,7 @@ __device__ __forceinline__ void chunk_tables(const void* rawp, float* tab, int l
   float l2[TPL];
 #pragma unroll
   for (int k = 0; k < TPL; ++k) l2[k] = coef_log2<COEF>(v[k]);
-  tables_from_log2<TL, BWD>(l2, tab, lane, carry_scale);
+  tables_from_log2<TL, BWD>(l2, tab, tab2, lane, carry_scale);
 }
 
 // Halo: a 16x16 block that belongs to a neighbouring warp's range is read straight from global
@@ -580,13 +592,14 @@ template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX
 __global__ void __launch_bounds__(WARPS * 32)
 btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                    const __grid_constant__ CUtensorMap tm_c, const KernelParams p) {
-  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false, OUT_F32>;
   constexpr int TL = LAYOUT::kTL;
   constexpr int NT = LAYOUT::kTiles;
   // Loads run AHEAD chunks in front of the one being computed.  A bf16 output leaves through the
   // stage buffer itself, so a stage is reloaded only two chunks after its store was issued.
   constexpr int AHEAD = OUT_F32 ? STAGES - 1 : STAGES - 2;
   static_assert(AHEAD >= 1, "need more stages");
+  static_assert(LAYOUT::kRawStages == AHEAD + 1, "a chunk's coefficients are consumed at its start");
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31;
@@ -645,7 +658,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   constexpr uint32_t kChunkBytes = LAYOUT::kXBytes + LAYOUT::kRawBytes;
   LaneCopy ld;
   if (lane < NBOX) ld.set(&tm_x, ws.x(0) + lane * 2048, LAYOUT::kXBytes, STAGES, 64 * lane, 16);
-  else ld.set(&tm_c, ws.raw_addr(0), LAYOUT::kRawBytes, STAGES, 0, 1);
+  else ld.set(&tm_c, ws.raw_addr(0), LAYOUT::kRawBytes, LAYOUT::kRawStages, 0, 1);
   auto issue = [&]() {  // starts the loads of the producer cursor's chunk into stage s_prod, then advances
     const uint32_t bar = ws.bar(s_prod);
     if (lane <= NBOX) {
@@ -661,7 +674,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   float cg = 0.0f, cg8 = 0.0f;  // carry into the next block, channels g and g+8
   bool failed = false;
-  int j = 0, s = 0;
+  int j = 0, s = 0;  // chunk, its stage in the x ring
   uint32_t phase = 0;
   // HANDOFF: the run in work is this warp's krun-th; its first block waits, uncorrected, for the carry from the left
   int krun = 0;
@@ -673,6 +686,12 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   for (; j < n; ++j) {
     if (j + AHEAD < n) {
       if (!OUT_F32 && lane < NBOX) bulk_wait_group_read<1>();  // this lane's store that last used that stage has drained
+      if constexpr (OUT_F32 && LAYOUT::kTInPlace) {
+        // the coefficient buffer about to be reloaded was last WRITTEN by this warp (the T table of the chunk
+        // before); with a 16-bit output the fence in front of the chunk's store already orders that
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
       issue();
     }
     // the decision to give up is taken by the whole warp: the code below is full of warp-wide instructions
@@ -682,8 +701,13 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
     const int nt = chunk_tiles<TL, RAGGED>(cons.cs, L);
     const int c0 = cons.cs * TL;
-    float* tab = ws.tab_ptr(0);
-    chunk_tables<COEF, TL, false, F16>(ws.raw_ptr(s), tab, lane, carry_scale);
+    // the chunk's stage in the coefficient ring, which is as long as the x ring or has two stages
+    static_assert(LAYOUT::kRawStages == STAGES || LAYOUT::kRawStages == 2, "coefficient ring");
+    const int rs = LAYOUT::kRawStages == STAGES ? s : (j & 1);
+    // T over the raw coefficients when they are floats, else in front of P in the table area
+    float* tab = LAYOUT::kTInPlace ? reinterpret_cast<float*>(ws.raw_ptr(rs)) : ws.tab_ptr(0);
+    float* tabP = LAYOUT::kTInPlace ? ws.tab_ptr(0) : ws.tab_ptr(0) + TL;
+    chunk_tables<COEF, TL, false, F16>(ws.raw_ptr(rs), tab, tabP, lane, carry_scale);
 
     if (cons.cs == 0 || !p.use_carry) {
       cg = cg8 = 0.0f;
@@ -700,6 +724,7 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
     const float* tg = tab + tl.g;
     const float* tt = tab + 2 * tl.t;
+    const float* tp = tabP + 2 * tl.t;
     const uint32_t xs = ws.x(s);
     const uint32_t ldm = xs + tl.ldm_base;
     const uint32_t stb = xs + tl.st_base;
@@ -734,8 +759,8 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           Act<F16>::mma8(v0, a0, a1, lf.b00);
           Act<F16>::mma16(v1, a0, a1, a2, a3, lf.b10, lf.b11);
         }
-        const float2 Pa = *reinterpret_cast<const float2*>(tt + TL + 16 * i);
-        const float2 Pb = *reinterpret_cast<const float2*>(tt + TL + 16 * i + 8);
+        const float2 Pa = *reinterpret_cast<const float2*>(tp + 16 * i);
+        const float2 Pb = *reinterpret_cast<const float2*>(tp + 16 * i + 8);
         // y = v + P (x) carry, a token pair per packed fp32x2 instruction (the accumulators hold tokens
         // 2t, 2t+1 of a channel side by side)
         const float2 cg2 = make_float2(cg, cg), cg82 = make_float2(cg8, cg8);
@@ -1110,7 +1135,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const int nt = chunk_tiles<TL, RAGGED>(cons.cs, L);
     const int c0 = cons.cs * TL;
     float* tab = ws.tab_ptr(tset);
-    chunk_tables<COEF, TL, true, F16>(ws.raw_ptr(s), tab, lane, carry_scale);
+    chunk_tables<COEF, TL, true, F16>(ws.raw_ptr(s), tab, tab + TL, lane, carry_scale);
     if (j == 0 && cons.cs != 0 && p.use_carry) {
       halo_reduce<COEF, false, false, PRECISE, F16>(p.x, p.coeff, L, cons.bh, c0 - 16, lane, vl_g, vl_g8);
     }

@@ -286,7 +286,7 @@ bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) !
 template <int COEF, bool F16>
 int launch_forward_handoff(const void* coeff, const void* x, void* y, Dims d, cudaStream_t stream, bool* done) {
   constexpr int NBOX = 2, STAGES = 3, WARPS = 4;
-  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false, false>;
   constexpr int kSmem = LAYOUT::kBytes + WARPS * kSeamBytesPerWarp;
   auto kern = btp_forward_kernel<COEF, false, false, false, true, NBOX, STAGES, WARPS, F16, true>;
   static Launcher<decltype(kern)> L(kern, kSmem, WARPS * 32);
@@ -362,7 +362,7 @@ int launch_forward_handoff(const void* coeff, const void* x, void* y, Dims d, cu
 // ------------------------------------------------------------------ forward dispatch
 template <int COEF, bool OUT_F32, bool CKPT, bool RAGGED, bool PRECISE, int NBOX, int STAGES, int WARPS, bool F16>
 int launch_forward_impl(const void* coeff, const void* x, void* y, float* ckpt, Dims d, int k, cudaStream_t stream) {
-  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false>;
+  using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false, OUT_F32>;
   if constexpr (!OUT_F32 && !CKPT && !RAGGED && PRECISE && NBOX == 2 && STAGES == 3 && WARPS == 4) {
     if (k == 2 && g_seam_mode.load(std::memory_order_relaxed) == BTP_SEAM_HANDOFF) {
       bool done = false;
