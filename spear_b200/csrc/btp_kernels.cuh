@@ -656,6 +656,10 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   // A ragged last chunk is fetched whole as well: what lies beyond the sequence arrives as zeros and still
   // counts towards the barrier's byte count, so the count is a constant.
   constexpr uint32_t kChunkBytes = LAYOUT::kXBytes + LAYOUT::kRawBytes;
+  // The outputs are what the next kernel of the stream reads: their lines are marked to leave L2 last.  (Measured:
+  // the forward 2 % faster in its own loop, the forward+backward step 1 - 2.5 % faster, the backward 1 % slower in
+  // its own loop; marking the loads, either way, was slower.)
+  const uint64_t keep_out = l2_policy_evict_last();
   LaneCopy ld;
   if (lane < NBOX) ld.set(&tm_x, ws.x(0) + lane * 2048, LAYOUT::kXBytes, STAGES, 64 * lane, 16);
   else ld.set(&tm_c, ws.raw_addr(0), LAYOUT::kRawBytes, LAYOUT::kRawStages, 0, 1);
@@ -814,7 +818,9 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       fence_proxy_async_smem();
       __syncwarp();
       if (lane < NBOX) {  // lane b sends box b (the same lane reloads that box's buffer later)
-        if (!RAGGED || c0 + 64 * lane < L) tma_store_2d(&tm_y, c0 + 64 * lane, cons.bh * 16, xs + lane * 2048);
+        if (!RAGGED || c0 + 64 * lane < L) {
+          tma_store_2d_hint(reinterpret_cast<uint64_t>(&tm_y), c0 + 64 * lane, cons.bh * 16, xs + lane * 2048, keep_out);
+        }
         bulk_commit_group();
       }
     }
@@ -947,6 +953,7 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
   else if (lane < NBOX + NDY) ld.set(&tm_dy, ws.dy(0) + (lane - NBOX) * 2048, LAYOUT::kDyBytes, STAGES - 1,
                                      (DY_F32 ? 32 : 64) * (lane - NBOX), 16);
   else ld.set(&tm_c, ws.raw_addr(0), LAYOUT::kRawBytes, STAGES, 0, 1);
+  const uint64_t keep_out = l2_policy_evict_last();  // as in the forward: the outputs leave L2 last
   // Stores of a chunk: lanes 0 .. NBOX-1 its dx boxes (out of the x buffers), lane NBOX its row of dA.
   LaneCopy st;
   if (lane < NBOX) st.set(&tm_dx, ws.x(0) + lane * 2048, LAYOUT::kXBytes, STAGES, 64 * lane, 16);
@@ -1112,7 +1119,9 @@ btp_backward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     __syncwarp();
     if (lane <= NBOX) {
       // a ragged chunk is stored whole too: the copy clips what lies beyond the sequence
-      if (!RAGGED || p_c0 + st.col_off < L) tma_store_2d(st.map, p_c0 + st.col_off, p_bh * st.row_mul, st.at(p_stage));
+      if (!RAGGED || p_c0 + st.col_off < L) {
+        tma_store_2d_hint(st.map, p_c0 + st.col_off, p_bh * st.row_mul, st.at(p_stage), keep_out);
+      }
       bulk_commit_group();
     }
   };

@@ -157,6 +157,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, uint64_t map, int c0, 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   tma_load_2d(dst, reinterpret_cast<uint64_t>(map), c0, c1, bar);
 }
+// L2 eviction-priority policy for the stores below that take one.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_store_2d_hint(uint64_t map, int c0, int c1, uint32_t src, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;" ::"l"(map),
+               "r"(c0), "r"(c1), "r"(src), "l"(policy)
+               : "memory");
+}
 // 2-D tiled store shared -> global (bulk async-group).
 __device__ __forceinline__ void tma_store_2d(uint64_t map, int c0, int c1, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0),
