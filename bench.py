@@ -53,7 +53,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one backward launch at this workload, from an ncu capture of
 # this command with one input set: 276.9 MB read + 114.0 MB written (the remaining 37 MB of the 151 MB of
 # output were still in L2 when the single profiled launch ended).
-BWD_TRAFFIC_BYTES = 390_901_504
+BWD_TRAFFIC_BYTES = 390_839_040
 METRIC = "btp_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
