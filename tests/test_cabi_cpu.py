@@ -53,6 +53,25 @@ def test_abi_version_and_status_strings(lib):
         assert name in text
 
 
+def test_seam_mode_and_launch_shape_are_host_state(lib):
+    """btp_sm100_set_seam_mode returns the previous mode, ignores values it does not know, and the launch-shape
+    diagnostic reads zeros on a thread that has launched nothing (no GPU is touched by either)."""
+    from spear_b200 import _lib
+
+    header = open(HEADER).read()
+    assert "#define BTP_SEAM_RECOMPUTE 0" in header and "#define BTP_SEAM_HANDOFF 1" in header
+    assert (_lib.SEAM_RECOMPUTE, _lib.SEAM_HANDOFF) == (0, 1)
+    assert lib.btp_sm100_set_seam_mode(_lib.SEAM_HANDOFF) == _lib.SEAM_RECOMPUTE  # the default
+    assert lib.btp_sm100_set_seam_mode(7) == _lib.SEAM_HANDOFF  # unknown value: nothing changes
+    assert lib.btp_sm100_set_seam_mode(-1) == _lib.SEAM_HANDOFF
+    assert _lib.set_seam_mode(_lib.SEAM_RECOMPUTE) == _lib.SEAM_HANDOFF
+    assert lib.btp_sm100_set_seam_mode(_lib.SEAM_RECOMPUTE) == _lib.SEAM_RECOMPUTE
+    with pytest.raises(ValueError):
+        _lib.set_seam_mode(2)
+    assert _lib.last_launch() == (0, 0)
+    lib.btp_sm100_last_launch(None, None)  # either pointer may be NULL
+
+
 def _fwd(lib, coeff=16, x=16, y=16, ck=0, B=1, H=1, L=16, k=2, cd=0, od=0):
     p = ctypes.c_void_p
     return lib.btp_sm100_forward(p(coeff), p(x), p(y), p(ck), B, H, L, k, cd, od, p(0))
