@@ -20,7 +20,9 @@
 //     contiguous range; forward: short runs of chunks dealt round-robin, so that the whole GPU works on
 //     one small moving window of memory).  No block-wide or grid-wide synchronisation exists, so no
 //     warp ever waits for another warp; the only waits are on the warp's own TMA loads (bounded) and
-//     on the previous kernel of the stream (griddepcontrol.wait, see the launch code).
+//     on the previous kernel of the stream (griddepcontrol.wait, see the launch code).  The one exception
+//     is the forward's optional HANDOFF variant (SeamLink below), where a warp waits, bounded as well, for
+//     the carry its left neighbour hands over inside a thread-block cluster.
 //   * Once per chunk the warp turns the coefficients into the per-token tables the blocks need
 //     (T, P, and for backward P shifted by one token and the last Lmat row), so that the per-block
 //     work is the Lmat fragment (6 exponentials per lane), the tensor-core products and FMAs.
@@ -29,6 +31,8 @@
 //   * The carry stays in registers while a warp walks along a sequence.  Where a warp's range
 //     starts (ends) inside a sequence the neighbouring block is re-read from global memory
 //     (16x16 values, a "halo") and its carry (dCarry) recomputed, so no seam ever drops a carry.
+//   * The plain backward deals whole sequences from the end of the batch; its TMA stores and the forward's
+//     mark their lines to leave L2 last (the outputs are what the next kernel reads).
 //   * Outputs in bf16 are written over the consumed input tile in shared memory and leave with a
 //     TMA store; fp32 outputs are stored straight from the accumulator fragments (32-byte runs).
 #pragma once
