@@ -290,16 +290,21 @@ def main():
             out.append((a, x, dy, torch.empty_like(x), torch.empty_like(x), torch.empty(nb, heads, length, device=dev)))
         return out
 
-    def loop_us(launch, n, repeats):
+    def loop_us(launch, n, repeats, idle_s=0.0):
         """n back-to-back launches between two CUDA events on the launching stream, `repeats` times ->
         us per launch of every repeat.  This is the kernel's launch duration the way it runs in a step loop
-        (launch latency hidden behind the previous kernel)."""
+        (launch latency hidden behind the previous kernel).  With `idle_s` the GPU idles that long before every
+        repeat: the kernel timed alone, as a burst, rather than at the clock the loops before it left behind."""
         res = []
         for i in range(3):
             launch(i)
         for _ in range(repeats):
             g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            if idle_s > 0:
+                time.sleep(idle_s)
+                launch(0)  # wakes the clocks; untimed
+                torch.cuda.synchronize()
             g0.record()
             for i in range(n):
                 launch(i)
@@ -360,6 +365,10 @@ def main():
         evs[i][2].record()
     barrier()
     clocks = sampler.stop()
+    # the same loops as bursts: 0.3 s of idle before each repeat (extra keys; `frac` stays on the loops above, and
+    # the clock record, which ends here, covers those and the timed steps)
+    fwd_burst = statistics.median(loop_us(launch_fwd, nk, reps, idle_s=0.3))
+    bwd_burst = statistics.median(loop_us(launch_bwd, nk, reps, idle_s=0.3))
     fwd_single_us = statistics.mean(e[0].elapsed_time(e[1]) for e in evs) * 1e3
     bwd_single_us = statistics.mean(e[1].elapsed_time(e[2]) for e in evs) * 1e3
     _lib.device_status()
@@ -515,8 +524,9 @@ def main():
 
     # ---- max over ranks
     if dist is not None:
-        total_ms, e2e_ms, e2e_autograd_ms, floor_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us = max_over_ranks(
-            [total_ms, e2e_ms, e2e_autograd_ms, floor_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us], device=dev)
+        (total_ms, e2e_ms, e2e_autograd_ms, floor_ms, fwd_us, bwd_us, fwd_single_us, bwd_single_us, fwd_burst,
+         bwd_burst) = max_over_ranks([total_ms, e2e_ms, e2e_autograd_ms, floor_ms, fwd_us, bwd_us, fwd_single_us,
+                                      bwd_single_us, fwd_burst, bwd_burst], device=dev)
         launches = int(sum_over_ranks([launches], device=dev)[0])
 
     if rank == 0:
@@ -560,16 +570,19 @@ def main():
                          "traffic": BWD_TRAFFIC_BYTES if (B, H, L) == (1024, 32, 128) else None,
                          "peak_kind": f"of {peak_kind}", "us_per_launch": bwd_us, "us_per_launch_best": min(bwd_runs),
                          "frac_best_repeat": bwd_b * ht / (min(bwd_runs) * 1e-6) / 1e9 / peak,
+                         "us_per_launch_burst": bwd_burst, "frac_burst": bwd_b * ht / (bwd_burst * 1e-6) / 1e9 / peak,
                          "us_per_launch_runs": bwd_runs,
                          "us_per_launch_between_event_records": bwd_single_us,
                          "method": f"{nk} back-to-back launches of the kernel between two CUDA events on the launching stream, "
                                    f"median of {reps} repeats (frac_best_repeat: the best of them, the way the measured "
-                                   "peak is the best of 10 copies)",
+                                   "peak is the best of 10 copies; frac_burst: the same loops, median, each after 0.3 s of idle)",
                          "algorithmic_bytes_per_launch": bwd_b * ht},
             "roofline_forward": {"bound": "hbm", "kernel": "btp_forward_kernel", "achieved": fwd_gbs, "peak": peak,
                                  "unit": "GB/s", "frac": fwd_gbs / peak, "us_per_launch": fwd_us,
                                  "us_per_launch_best": min(fwd_runs), "us_per_launch_runs": fwd_runs,
                                  "frac_best_repeat": fwd_b * ht / (min(fwd_runs) * 1e-6) / 1e9 / peak,
+                                 "us_per_launch_burst": fwd_burst,
+                                 "frac_burst": fwd_b * ht / (fwd_burst * 1e-6) / 1e9 / peak,
                                  "us_per_launch_between_event_records": fwd_single_us,
                                  "algorithmic_bytes_per_launch": fwd_b * ht},
             "step_hbm": {"achieved_gbs": step_gbs, "frac_of_measured": step_gbs / peak,
