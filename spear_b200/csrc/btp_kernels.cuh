@@ -561,8 +561,12 @@ __device__ __forceinline__ void report_error(unsigned int code, int warp, int ch
 //     on the neighbour's mbarrier), then waits (bounded) for its own slot to fill.
 //   * Two slots per warp, used alternately; before a slot is written a second time the writer waits (bounded) for the
 //     credit the reader sends when it has read the slot (an arrive on an mbarrier of the writer).
-// Per warp: 2 x 64 bytes of landing slots, 2 "slot full" barriers, 2 "credit" barriers.
+//   * A warp that gives up (a bounded wait ran out) sets an abort word in every CTA of its cluster; the waits for
+//     a hand-off or a credit look at their CTA's word and give up with it, so that one failure ends the kernel
+//     after one wait limit, not after one limit per warp of the chain.
+// Per warp: 2 x 64 bytes of landing slots, 2 "slot full" barriers, 2 "credit" barriers; per CTA: the abort word.
 constexpr int kSeamBytesPerWarp = 2 * 64 + 2 * 8 + 2 * 8;
+constexpr int kSeamBytesPerCta = 16;
 struct SeamLink {
   uint32_t slot;        // own landing slots (shared::cta address), 64 bytes each: [g][2] floats = channels g, g+8
   uint32_t full;        // own "slot full" barriers
@@ -570,7 +574,9 @@ struct SeamLink {
   uint32_t right_slot;  // right neighbour's landing slots / "slot full" barriers, left neighbour's credit barriers
   uint32_t right_full;  //   (cluster-wide shared addresses)
   uint32_t left_credit;
+  uint32_t abort_word;  // own CTA's abort word (shared::cta address)
   __device__ __forceinline__ void set(uint32_t seam_base, int warp, int warps) {
+    abort_word = seam_base + static_cast<uint32_t>(warps) * kSeamBytesPerWarp;
     const uint32_t rank = cluster_cta_rank();
     const auto at = [&](int w) { return seam_base + static_cast<uint32_t>(w) * kSeamBytesPerWarp; };
     slot = at(warp);
@@ -621,7 +627,10 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const int n = forward_work(wid, nwarps, p, cons);
   static_assert(!HANDOFF || (!OUT_F32 && !CKPT && !RAGGED), "the hand-off variant covers full chunks and 16-bit outputs");
   SeamLink seam;
-  if constexpr (HANDOFF) seam.set(smem_u32(smem_raw) + LAYOUT::kBytes, warp, WARPS);
+  if constexpr (HANDOFF) {
+    seam.set(smem_u32(smem_raw) + LAYOUT::kBytes, warp, WARPS);
+    if (threadIdx.x == 0) st_shared_u32(seam.abort_word, 0u);  // visible cluster-wide after the first barrier below
+  }
   // With HANDOFF every thread of the cluster passes two cluster-wide barriers: one after the barriers are
   // initialised (nobody writes into a CTA that has not set up yet), one before leaving (nobody leaves while a
   // neighbour may still write into its shared memory).  A warp without work passes both right away.
@@ -838,7 +847,9 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const uint32_t use = static_cast<uint32_t>(krun >> 1);
         if (p.use_carry && cons.cs != ncs - 1) {  // the run to the right is waiting for (cg, cg8)
           bool ok = true;
-          if (krun >= 2) ok = mbar_wait_bounded_cluster(seam.credit + 8 * sl, (use - 1) & 1u, p.wait_limit_ns);
+          if (krun >= 2) {
+            ok = mbar_wait_bounded_cluster(seam.credit + 8 * sl, (use - 1) & 1u, p.wait_limit_ns, seam.abort_word);
+          }
           if (!__all_sync(0xffffffffu, ok)) {
             failed = true;
             break;
@@ -846,7 +857,8 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           if (tl.t == 0) st_async_f32x2(seam.right_slot + 64 * sl + 8 * tl.g, cg, cg8, seam.right_full + 8 * sl);
         }
         if (owed) {
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded_cluster(seam.full + 8 * sl, use & 1u, p.wait_limit_ns))) {
+          if (!__all_sync(0xffffffffu,
+                          mbar_wait_bounded_cluster(seam.full + 8 * sl, use & 1u, p.wait_limit_ns, seam.abort_word))) {
             failed = true;
             break;
           }
@@ -882,6 +894,9 @@ btp_forward_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   if (failed) {
     if (lane == 0) report_error(1u, warp, cons.bh * ncs + cons.cs);
+    if constexpr (HANDOFF) {  // nobody in the cluster needs to wait for this warp any longer
+      if (lane < cluster_cta_count()) st_cluster_u32(map_to_cta(seam.abort_word, lane), 1u);
+    }
     // give the loads still in flight a (bounded) chance to land before the buffers are released
     for (int k = j; k < n && k <= j + AHEAD; ++k) {
       mbar_wait_bounded(ws.bar(s), phase, p.wait_limit_ns);

@@ -113,7 +113,11 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
+// `abort_word`: shared-memory address of a word that a warp of the cluster sets when it has given up; the wait
+// then gives up as well instead of sitting out its own limit (a chain of warps waiting for one another would
+// otherwise take the limit once per link).
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, unsigned long long limit_ns,
+                                                          uint32_t abort_word) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (;;) {
@@ -121,8 +125,14 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait_cluster(bar, parity)) return true;
     }
-    if (global_timer_ns() - t0 > limit_ns) return false;
+    uint32_t stop;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(stop) : "r"(abort_word) : "memory");
+    if (stop != 0 || global_timer_ns() - t0 > limit_ns) return false;
   }
+}
+// Plain store into the shared memory of a CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_cluster_u32(uint32_t remote_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote_addr), "r"(v) : "memory");
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch

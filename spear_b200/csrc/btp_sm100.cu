@@ -287,7 +287,7 @@ template <int COEF, bool F16>
 int launch_forward_handoff(const void* coeff, const void* x, void* y, Dims d, cudaStream_t stream, bool* done) {
   constexpr int NBOX = 2, STAGES = 3, WARPS = 4;
   using LAYOUT = SmemLayout<COEF, NBOX, STAGES, WARPS, false, false, false>;
-  constexpr int kSmem = LAYOUT::kBytes + WARPS * kSeamBytesPerWarp;
+  constexpr int kSmem = LAYOUT::kBytes + WARPS * kSeamBytesPerWarp + kSeamBytesPerCta;
   auto kern = btp_forward_kernel<COEF, false, false, false, true, NBOX, STAGES, WARPS, F16, true>;
   static Launcher<decltype(kern)> L(kern, kSmem, WARPS * 32);
   *done = false;

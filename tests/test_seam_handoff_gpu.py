@@ -145,20 +145,28 @@ def _forward_recompute(lib, a, x, tag):
 
 
 def test_a_handoff_that_never_arrives_is_given_up_and_reported(handoff):
-    """Warp 0 of block 0 loses its first load (test hook) and gives up, so it never hands its carry on: the warp to
-    its right waits for it, gives up after the limit as well, and the kernel ends.  Nothing hangs, the context
-    stays usable, the error is reported, and the next launch is right."""
+    """Warp 0 of block 0 loses its first load (test hook) and gives up, so it never hands its carry on.  It sets the
+    abort word of its cluster, the warps waiting for a hand-off down the chain give up with it, and the kernel ends
+    after about ONE wait limit (not one per warp of the chain).  Nothing hangs, the context stays usable, the error
+    is reported, and the next launch is right."""
     from spear_b200 import _lib
 
     lib = handoff
     a, x, tag = _inputs(16, 37, 4096, "16bit", torch.bfloat16, seed=9)
     detail = (ctypes.c_uint * 4)()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    previous = lib.btp_sm100_set_wait_limit(2_000_000)  # 2 ms
+    limit_ms = 20
+    previous = lib.btp_sm100_set_wait_limit(limit_ms * 1_000_000)
     try:
         lib.btp_sm100_test_expect_missing_bytes(64)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
         _forward(lib, a, x, tag)
+        t1.record()
+        torch.cuda.synchronize()
         assert _lib.last_launch()[1] == 4
+        # 16 warps share a sequence: one limit each down the chain would be 16 x 20 ms
+        assert limit_ms <= t0.elapsed_time(t1) < 4 * limit_ms, t0.elapsed_time(t1)
         rc = lib.btp_sm100_device_status(stream, detail)
         assert rc == -8 and list(detail)[0] == 1 and list(detail)[1] == 0  # a timeout, in block 0
         assert lib.btp_sm100_device_status(stream, detail) == 0
