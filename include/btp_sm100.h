@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define BTP_SM100_ABI_VERSION 3
+#define BTP_SM100_ABI_VERSION 4
 
 /* status codes */
 #define BTP_OK 0

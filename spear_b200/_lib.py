@@ -24,7 +24,7 @@ ACT_F16 = 0x10  # flag on a float coefficient tag: the activations are float16
 SEAM_RECOMPUTE = 0  # forward: the carry across a seam is recomputed from the block to the left (default)
 SEAM_HANDOFF = 1    # forward: the carry is handed over through distributed shared memory inside a cluster
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # every symbol include/btp_sm100.h declares: name -> (restype, argtypes)
 _vp, _i, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong

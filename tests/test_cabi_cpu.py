@@ -40,7 +40,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version_and_status_strings(lib):
-    assert lib.btp_sm100_abi_version() == 3
+    assert lib.btp_sm100_abi_version() == 4
     seen = set()
     for code in range(0, -10, -1):
         name = lib.btp_sm100_status_string(code).decode()
